@@ -4,7 +4,8 @@ per *group* of cache entries, and slots of fixed-size state.  Pure Python, no te
 Cache entries (one per layer call that keeps something) with equal needs form a group.
 Every paged group has pages of its own: its own pool, its own block table per request.
 A group whose entries read only a window of keys gives pages back as soon as the window
-has passed them (likewise a group whose entries read only the chunk of positions they stand in);
+has passed them (likewise a group whose entries read only the chunk of positions they stand in;
+the pages of first keys that stay visible beside the window are held to the end);
 a request that ends gives back everything.  Freed pages go to the back
 of the pool and are handed out again from the front, with whatever they still contain
 (``emberserve/kv/block_manager.py:69-72,132-152``: same deque discipline, same
@@ -143,6 +144,9 @@ class CacheManager:
         self.pools = [PagePool(n) for n in counts]
         self.windows: list[int | None] = [self.groups[i].need.window for i in self.paged_groups]
         self.chunks: list[int | None] = [getattr(self.groups[i].need, "chunk", None) for i in self.paged_groups]
+        # leading pages that are never given back: they hold first keys that every later query reads
+        self.kept_pages: list[int] = [-(-int(getattr(self.groups[i].need, "keep_first", 0) or 0) // page_size)
+                                      for i in self.paged_groups]
         self.num_state_slots = num_state_slots if self.state_groups else 0
         self._free_slots: deque[int] = deque(range(self.num_state_slots))
         self._fresh_slots: set[int] = set()
@@ -258,7 +262,7 @@ class CacheManager:
                 first_needed = max(first_needed, (seq.committed // chunk) * chunk)
             upto = min(first_needed // self.page_size, len(seq.tables[k]))
             table = seq.tables[k]
-            for i in range(seq.released[k], upto):
+            for i in range(max(seq.released[k], self.kept_pages[k]), upto):
                 self.pools[k].give(table[i])
                 table[i] = -1
                 seq.arrays[k][i] = 0

@@ -2,7 +2,8 @@
 
 A paged group with E entries holds one tensor ``[E, 2, num_pages, kv_heads, page_size,
 head_dim]`` (2 = keys, values), so the keys of one (page, KV head) are one contiguous tile
-of ``page_size * head_dim`` elements; a group of latent vectors (``PagedLatent``) holds
+of ``page_size * head_dim`` elements (where value heads have another size than key heads, an
+entry is one flat run of memory: all key pages, then all value pages); a group of latent vectors (``PagedLatent``) holds
 ``[E, num_pages, page_size, dim]``.  The reference keeps ``[num_blocks, block_size,
 kv_heads, head_dim]`` per layer (``emberserve/kv/cache.py:30-34``); the geometry (pages of
 ``block_size`` token slots, slot = page * page_size + offset) is the same.  Contents are
@@ -37,6 +38,10 @@ class CacheStorage:
                 n = num_pages[paged_seen]
                 if isinstance(g.need, PagedLatent):
                     t = torch.zeros(len(g.entries), n, page_size, g.need.dim, dtype=dtype, device=self.device)
+                elif g.need.value_dim != g.need.head_dim:
+                    per_page = g.need.num_kv_heads * page_size
+                    t = torch.zeros(len(g.entries), n * per_page * (g.need.head_dim + g.need.value_dim),
+                                    dtype=dtype, device=self.device)
                 else:
                     assert isinstance(g.need, PagedKV)
                     t = torch.zeros(len(g.entries), 2, n, g.need.num_kv_heads, page_size, g.need.head_dim,
@@ -84,8 +89,15 @@ class CacheStorage:
         need = self.groups[gi].need
         t = self.tensors[gi]
         if isinstance(need, PagedKV):
-            return PagedKVHandle(k=t[j, 0], v=t[j, 1], block_tables=block_tables[pk],
-                                 page_size=self.page_size, window=need.window, write=write, chunk=need.chunk)
+            if need.value_dim != need.head_dim:
+                slots = t.shape[1] // (need.head_dim + need.value_dim)  # pages * kv_heads * page_size
+                pages = slots // (need.num_kv_heads * self.page_size)
+                k = t[j, :slots * need.head_dim].view(pages, need.num_kv_heads, self.page_size, need.head_dim)
+                v = t[j, slots * need.head_dim:].view(pages, need.num_kv_heads, self.page_size, need.value_dim)
+            else:
+                k, v = t[j, 0], t[j, 1]
+            return PagedKVHandle(k=k, v=v, block_tables=block_tables[pk], page_size=self.page_size,
+                                 window=need.window, write=write, chunk=need.chunk, keep_first=need.keep_first)
         if isinstance(need, PagedLatent):
             return PagedLatentHandle(pages=t[j], block_tables=block_tables[pk], page_size=self.page_size,
                                      window=need.window, write=write)

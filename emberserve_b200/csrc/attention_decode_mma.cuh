@@ -31,7 +31,15 @@ struct DecodeParams {
     const float* sinks = nullptr;   // [nh]: exp(sinks[h]) joins the softmax's denominator
     const bf16* gate = nullptr;     // [N, gate_stride]: head h's output times sigmoid(gate[n, h])
     long long gate_stride = 0;
+    int keep = 0;                   // > 0: keys j < keep stay visible beside the window
+    const float* out_table = nullptr;  // [positions, D / 2, (cos, sin)]: the result is turned back by the query's position
+    int out_pairing = 0;            // 0: pair (i, i + D / 2); 1: pair (2 i, 2 i + 1)
+    const int* positions = nullptr; // [N] position of each token of the step
 };
+
+// Whether the tensor-core kernels for masked attention take these options (all of them take chunk, sinks
+// and gate; kept first keys and a result that is turned back are taken by the generic kernel alone).
+inline bool masked_mma_takes(const DecodeParams& p) { return p.keep == 0 && p.out_table == nullptr; }
 
 // The first key that the query at position p may see.
 __host__ __device__ __forceinline__ int first_visible(int p, int window, int chunk) {

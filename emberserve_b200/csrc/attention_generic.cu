@@ -42,7 +42,21 @@ struct AttnParams {
     const float* sinks = nullptr;   // [nh] float: exp(sinks[h]) joins the softmax's denominator (no key, no value)
     const void* gate = nullptr;     // [N, gate_stride]: head h's output is multiplied by sigmoid(gate[n, h])
     long long gate_stride = 0;
+    int keep = 0;                   // > 0: keys j < keep stay visible to every later query, whatever the window says
+    int DV = 0;                     // numbers per value head (the caches may differ in their last dimension)
+    // Values that were turned by their own position before they were cached: the sum over the values is
+    // turned back by the query's position.  out_table: [positions, DV / 2, (cos, sin)]; pair i is
+    // (i, i + DV / 2) or, with out_pairing 1, (2 i, 2 i + 1).
+    const float* out_table = nullptr;
+    int out_pairing = 0;
+    const int* positions = nullptr; // [N] position of every token of the step (for the merge of key splits)
 };
+
+// The key tiles that a block walks when the first `keep` keys stay visible beside the window: `nhead`
+// tiles from position 0 (those that lie wholly before the window's first tile), then the tiles from kt0.
+__device__ __forceinline__ int tile_start(int t, int nhead, int kt0, int bk) {
+    return t < nhead ? t * bk : kt0 + (t - nhead) * bk;
+}
 
 template <typename T, int VEC> struct VecLoad;
 template <> struct VecLoad<float, 4> {
@@ -69,12 +83,12 @@ paged_attention_kernel(const AttnParams p) {
     constexpr int BQ = NWARPS * RPW;
     constexpr int VEC = 16 / sizeof(T);
     extern __shared__ float smem[];
-    const int D = p.D, G = p.G;
+    const int D = p.D, G = p.G, DV = p.DV;
     const int KST = D + 1;                       // K tile row stride (no bank conflicts)
     float* Qs = smem;                            // [BQ][D]
     float* Ks = Qs + BQ * D;                     // [BK][D+1]
-    float* Vs = Ks + BK * KST;                   // [BK][D]
-    float* Ps = Vs + BK * D;                     // [BQ][BK+1]
+    float* Vs = Ks + BK * KST;                   // [BK][DV]
+    float* Ps = Vs + BK * DV;                    // [BQ][BK+1]
 
     const int b = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
     const int hk = blockIdx.y;
@@ -90,7 +104,9 @@ paged_attention_kernel(const AttnParams p) {
     const int k_begin = first_visible(p_lo, p.window, p.chunk);
     const int k_end = p_hi + 1;
     const int kt0 = (k_begin / BK) * BK;
-    const int ntiles = (k_end - kt0 + BK - 1) / BK;
+    const int keep = min(p.keep, k_begin);       // kept keys that the window of the block's first query has passed
+    const int nhead = min((keep + BK - 1) / BK, kt0 / BK);
+    const int ntiles = nhead + (k_end - kt0 + BK - 1) / BK;
     const int tiles_per_split = (ntiles + p.splits - 1) / p.splits;
     const int t_begin = split * tiles_per_split;
     const int t_end = min(ntiles, t_begin + tiles_per_split);
@@ -129,26 +145,35 @@ paged_attention_kernel(const AttnParams p) {
     }
 
     for (int t = t_begin; t < t_end; ++t) {
-        const int kt = kt0 + t * BK;
+        const int kt = tile_start(t, nhead, kt0, BK);
         __syncthreads();  // previous tile fully consumed (and Qs written, first time)
         for (int idx = threadIdx.x * VEC; idx < BK * D; idx += NWARPS * 32 * VEC) {
             const int j = idx / D, d = idx % D;
             const int key = kt + j;
-            float kk[VEC], vv[VEC];
-            if (key >= k_begin && key < k_end) {
+            float kk[VEC];
+            if ((key >= k_begin || key < keep) && key < k_end) {
                 const int page = p.bt[(size_t)b * p.bt_stride + key / p.page_size];
-                const size_t off = (((size_t)page * p.nkv + hk) * p.page_size + key % p.page_size) * D + d;
-                VecLoad<T, VEC>::load(kc + off, kk);
-                VecLoad<T, VEC>::load(vc + off, vv);
+                VecLoad<T, VEC>::load(kc + (((size_t)page * p.nkv + hk) * p.page_size + key % p.page_size) * D + d, kk);
             } else {
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) { kk[i] = 0.f; vv[i] = 0.f; }
+                for (int i = 0; i < VEC; ++i) kk[i] = 0.f;
             }
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                Ks[j * KST + d + i] = kk[i];
-                Vs[j * D + d + i] = vv[i];
+            for (int i = 0; i < VEC; ++i) Ks[j * KST + d + i] = kk[i];
+        }
+        for (int idx = threadIdx.x * VEC; idx < BK * DV; idx += NWARPS * 32 * VEC) {
+            const int j = idx / DV, d = idx % DV;
+            const int key = kt + j;
+            float vv[VEC];
+            if ((key >= k_begin || key < keep) && key < k_end) {
+                const int page = p.bt[(size_t)b * p.bt_stride + key / p.page_size];
+                VecLoad<T, VEC>::load(vc + (((size_t)page * p.nkv + hk) * p.page_size + key % p.page_size) * DV + d, vv);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) vv[i] = 0.f;
             }
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) Vs[j * DV + d + i] = vv[i];
         }
         __syncthreads();
 
@@ -167,7 +192,7 @@ paged_attention_kernel(const AttnParams p) {
         const int key = kt + lane;
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
-            const bool visible = key <= qpos[r] && key >= qlo[r];
+            const bool visible = key <= qpos[r] && (key >= qlo[r] || key < p.keep);
             const float s = visible ? acc[r] * p.scale : -INFINITY;
             const float m_new = fmaxf(m[r], warp_max(s));
             const float pe = visible ? expf(s - m_new) : 0.f;
@@ -187,8 +212,8 @@ paged_attention_kernel(const AttnParams p) {
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int d = lane + 32 * c;
-                if (d < D) {
-                    const float vv = Vs[j * D + d];
+                if (d < DV) {
+                    const float vv = Vs[j * DV + d];
 #pragma unroll
                     for (int r = 0; r < RPW; ++r) o[r][c] = fmaf(pj[r], vv, o[r][c]);
                 }
@@ -198,6 +223,8 @@ paged_attention_kernel(const AttnParams p) {
     }
 
     // write out
+    const bool turn_back = p.out_table && p.splits == 1;
+    if (turn_back) __syncthreads();  // every warp is through with the last tile: Vs holds the rows now ([BQ][DV], BQ <= BK)
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
         const int gr = r0 + warp * RPW + r;
@@ -205,21 +232,39 @@ paged_attention_kernel(const AttnParams p) {
         const int tok = gr / G, head = hk * G + gr % G;
         const size_t prow = (size_t)(q0 + tok) * p.nh + head;
         if (p.splits == 1) {
-            T* dst = reinterpret_cast<T*>(p.out) + prow * D;
+            T* dst = reinterpret_cast<T*>(p.out) + prow * DV;
             float inv = 1.0f / (p.sinks ? l[r] + expf(p.sinks[head] - m[r]) : l[r]);
             if (p.gate)
                 inv *= 1.f / (1.f + expf(-to_f32<T>(reinterpret_cast<const T*>(p.gate)[(size_t)(q0 + tok) * p.gate_stride + head])));
+            if (turn_back) {
+                float* row = Vs + (size_t)(warp * RPW + r) * DV;
+#pragma unroll
+                for (int c = 0; c < DCH; ++c) {
+                    const int d = lane + 32 * c;
+                    if (d < DV) row[d] = o[r][c] * inv;
+                }
+                __syncwarp();
+                const int half = DV / 2;
+                const float* cs = p.out_table + (size_t)qpos[r] * half * 2;
+                for (int i = lane; i < half; i += 32) {
+                    const int ia = p.out_pairing ? 2 * i : i, ib = p.out_pairing ? 2 * i + 1 : i + half;
+                    const float cc = cs[2 * i], sn = cs[2 * i + 1], u = row[ia], w = row[ib];
+                    dst[ia] = from_f32<T>(u * cc + w * sn);
+                    dst[ib] = from_f32<T>(w * cc - u * sn);
+                }
+                continue;
+            }
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int d = lane + 32 * c;
-                if (d < D) dst[d] = from_f32<T>(o[r][c] * inv);
+                if (d < DV) dst[d] = from_f32<T>(o[r][c] * inv);
             }
         } else {
-            float* dst = p.part_o + (prow * p.splits + split) * D;
+            float* dst = p.part_o + (prow * p.splits + split) * DV;
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int d = lane + 32 * c;
-                if (d < D) dst[d] = o[r][c];
+                if (d < DV) dst[d] = o[r][c];
             }
             if (lane == 0) {
                 p.part_ml[(prow * p.splits + split) * 2] = m[r];
@@ -238,10 +283,13 @@ template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
                                        int splits, int D, const float* __restrict__ sinks, int nh,
-                                       const T* __restrict__ gate, long long gate_stride) {
+                                       const T* __restrict__ gate, long long gate_stride,
+                                       const float* __restrict__ out_table, int out_pairing,
+                                       const int* __restrict__ positions) {
     pdl_prologue();
     __shared__ float weight[MERGE_MAX_SPLITS];
     __shared__ float red[33];
+    __shared__ float row[256];  // the merged head before it is turned back (out_table; D <= 256)
     const size_t prow = blockIdx.x;
     const float* ml = part_ml + prow * splits * 2;
     // the splits' maxima and sums are read side by side (a thread per split), the partial
@@ -265,14 +313,26 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
         float acc = 0.f;
 #pragma unroll 8
         for (int s = 0; s < splits; ++s) acc += po[(size_t)s * D + d] * weight[s];  // in split order
-        out[prow * D + d] = from_f32<T>(acc * inv);
+        if (out_table) row[d] = acc * inv;
+        else out[prow * D + d] = from_f32<T>(acc * inv);
+    }
+    if (out_table) {
+        __syncthreads();
+        const int half = D / 2;
+        const float* cs = out_table + (size_t)positions[prow / nh] * half * 2;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const int ia = out_pairing ? 2 * i : i, ib = out_pairing ? 2 * i + 1 : i + half;
+            const float cc = cs[2 * i], sn = cs[2 * i + 1], u = row[ia], w = row[ib];
+            out[prow * D + ia] = from_f32<T>(u * cc + w * sn);
+            out[prow * D + ib] = from_f32<T>(w * cc - u * sn);
+        }
     }
 }
 
 template <typename T, int DCH, int RPW>
 int launch_attention(const AttnParams& p, int B, int max_q_len, cudaStream_t stream) {
     constexpr int BQ = NWARPS * RPW;
-    const size_t smem = sizeof(float) * ((size_t)BQ * p.D + (size_t)BK * (p.D + 1) + (size_t)BK * p.D +
+    const size_t smem = sizeof(float) * ((size_t)BQ * p.D + (size_t)BK * (p.D + 1) + (size_t)BK * p.DV +
                                          (size_t)BQ * (BK + 1));
     auto kernel = paged_attention_kernel<T, DCH, RPW>;
     if (smem > 48 * 1024) {
@@ -289,7 +349,7 @@ int launch_attention(const AttnParams& p, int B, int max_q_len, cudaStream_t str
 
 template <typename T, int RPW>
 int dispatch_dch(const AttnParams& p, int B, int max_q_len, cudaStream_t stream) {
-    switch ((p.D + 31) / 32) {
+    switch ((p.DV + 31) / 32) {
         case 1: return launch_attention<T, 1, RPW>(p, B, max_q_len, stream);
         case 2: return launch_attention<T, 2, RPW>(p, B, max_q_len, stream);
         case 3: return launch_attention<T, 3, RPW>(p, B, max_q_len, stream);
@@ -309,10 +369,10 @@ int run_attention(const AttnParams& p, int B, int N, int max_q_len, cudaStream_t
     const int rc = small ? dispatch_dch<T, 1>(p, B, max_q_len, stream)
                          : dispatch_dch<T, 4>(p, B, max_q_len, stream);
     if (rc != EMS_OK || p.splits == 1) return rc;
-    const int threads = p.D >= 128 ? 128 : 64;
+    const int threads = p.DV >= 128 ? 128 : 64;
     attention_merge_kernel<T><<<(unsigned)((size_t)N * p.nh), threads, 0, stream>>>(
-        p.part_o, p.part_ml, reinterpret_cast<T*>(p.out), p.splits, p.D, p.sinks, p.nh,
-        reinterpret_cast<const T*>(p.gate), p.gate_stride);
+        p.part_o, p.part_ml, reinterpret_cast<T*>(p.out), p.splits, p.DV, p.sinks, p.nh,
+        reinterpret_cast<const T*>(p.gate), p.gate_stride, p.out_table, p.out_pairing, p.positions);
     return launch_status();
 }
 
@@ -332,17 +392,21 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
                                int B, int N, int nh, int nkv, int D, int window, float scale,
                                int max_q_len, int splits, void* scratch, long long scratch_bytes,
                                int impl, int chunk, const float* sinks, const void* gate, long long gate_stride,
+                               int keep, int DV, const float* out_table, int out_pairing, const int* positions,
                                cudaStream_t stream) {
     // impl: 0 = the fastest kernel that takes the case, 1 = the generic kernel, 2 = the
     // tcgen05 prompt kernel or an error, 3 = the mma.sync kernels where they take the case.
     if (B <= 0 || N <= 0) return EMS_OK;
     const int esize = dtype == EMS_F32 ? 4 : 2;
     // (rows of a head are moved 16 bytes at a time)
-    if (D <= 0 || D % (16 / esize) || D > 256 || nkv <= 0 || nh % nkv || page_size <= 0 || splits < 1 ||
-        splits > MERGE_MAX_SPLITS || chunk < 0)
+    if (DV <= 0) DV = D;
+    if (D <= 0 || D % (16 / esize) || D > 256 || DV % (16 / esize) || DV > 256 || nkv <= 0 || nh % nkv ||
+        page_size <= 0 || splits < 1 || splits > MERGE_MAX_SPLITS || chunk < 0 || keep < 0 ||
+        (out_table && (DV % 2 || (splits > 1 && !positions))))
         return EMS_ERR_SHAPE;
+    if (window <= 0 && chunk <= 0) keep = 0;  // every key is visible anyway
     // the tensor-core kernels know the plain causal form (and a window)
-    const bool plain = chunk <= 0 && !sinks && !gate;
+    const bool plain = chunk <= 0 && !sinks && !gate && keep == 0 && DV == D && !out_table;
     if (!plain && impl == 2) return EMS_ERR_SHAPE;
     if ((q_stride * esize) % 16 || ((uintptr_t)q % 16) || ((uintptr_t)kcache % 16) || ((uintptr_t)vcache % 16))
         return EMS_ERR_ALIGN;
@@ -352,11 +416,12 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
     p.nh = nh; p.nkv = nkv; p.D = D; p.G = nh / nkv; p.window = window; p.splits = splits;
     p.scale = scale; p.part_o = nullptr; p.part_ml = nullptr;
     p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_stride = gate_stride;
+    p.keep = keep; p.DV = DV; p.out_table = out_table; p.out_pairing = out_pairing; p.positions = positions;
     if (splits > 1) {
-        if (scratch == nullptr || scratch_bytes < ems_paged_attention_scratch_bytes(N, nh, D, splits))
+        if (scratch == nullptr || scratch_bytes < ems_paged_attention_scratch_bytes(N, nh, DV, splits))
             return EMS_ERR_SCRATCH;
         p.part_o = reinterpret_cast<float*>(scratch);
-        p.part_ml = p.part_o + (size_t)N * nh * splits * D;
+        p.part_ml = p.part_o + (size_t)N * nh * splits * DV;
     }
     DecodeParams d;
     d.q = reinterpret_cast<const bf16*>(q); d.out = reinterpret_cast<bf16*>(out);
@@ -366,8 +431,15 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
     d.G = p.G; d.window = window; d.splits = splits;
     d.scale_log2 = scale * 1.4426950408889634f;
     d.chunk = chunk; d.sinks = sinks; d.gate = reinterpret_cast<const bf16*>(gate); d.gate_stride = gate_stride;
+    d.keep = keep; d.out_table = out_table; d.out_pairing = out_pairing; d.positions = positions;
     if (!plain) {
         // prompt portions on the tensor cores where the sizes allow; everything else on the generic kernel
+        const bool mma_form = DV == D && masked_mma_takes(d);
+        if (!mma_form) {
+            if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
+            if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);
+            return EMS_ERR_DTYPE;
+        }
         if ((impl == 0 || impl == 3) && splits == 1 && max_q_len > 1 &&
             prefill_mma_supported(dtype, D, q_stride, q, out, kcache, vcache) && (gate_stride * 2) % 2 == 0)
             return run_prefill_mma_masked(d, B, D, max_q_len, stream);
@@ -378,7 +450,7 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
             return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)N * nh)),
                               dim3(D >= 128 ? 128 : 64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml,
                               reinterpret_cast<bf16*>(out), splits, D, sinks, nh, reinterpret_cast<const bf16*>(gate),
-                              gate_stride);
+                              gate_stride, out_table, out_pairing, positions);
         }
         if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
         if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);
@@ -400,7 +472,8 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
         if (rc != EMS_OK || splits == 1) return rc;
         return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)N * nh)), dim3(D >= 128 ? 128 : 64),
                           0, stream, (const float*)p.part_o, (const float*)p.part_ml, reinterpret_cast<bf16*>(out),
-                          splits, D, (const float*)nullptr, nh, (const bf16*)nullptr, 0LL);
+                          splits, D, (const float*)nullptr, nh, (const bf16*)nullptr, 0LL, (const float*)nullptr, 0,
+                          (const int*)nullptr);
     }
     if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
     if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);
@@ -415,21 +488,26 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
                                    int impl, cudaStream_t stream) {
     return paged_attention_any(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride, page_size, cu_q,
                                starts, B, N, nh, nkv, D, window, scale, max_q_len, splits, scratch, scratch_bytes,
-                               impl, 0, nullptr, nullptr, 0, stream);
+                               impl, 0, nullptr, nullptr, 0, 0, D, nullptr, 0, nullptr, stream);
 }
 
-// The same with a chunk mask, a sink per head in the softmax's denominator and a sigmoid gate per
-// (token, head) on the output; each is optional (0 / null).
+// The same with a chunk mask, a sink per head in the softmax's denominator, a sigmoid gate per
+// (token, head) on the output, first keys that a window never hides (keep), value heads of another size
+// than the key heads (DV; vcache is [pages, nkv, page_size, DV] and out [N, nh * DV]) and values that were
+// turned by their positions when they were cached (out_table: the result is turned back by the query's
+// position, positions[n] of token n); each is optional (0 / null).
 EMS_EXPORT int ems_paged_attention_masked(const void* q, long long q_stride, void* out, int dtype,
                                           const void* kcache, const void* vcache, const int* block_tables,
                                           int bt_stride, int page_size, const int* cu_q, const int* starts,
                                           int B, int N, int nh, int nkv, int D, int window, int chunk,
                                           const float* sinks, const void* gate, long long gate_stride, float scale,
                                           int max_q_len, int splits, void* scratch, long long scratch_bytes,
-                                          int impl, cudaStream_t stream) {
+                                          int impl, int keep, int DV, const float* out_table, int out_pairing,
+                                          const int* positions, cudaStream_t stream) {
     return paged_attention_any(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride, page_size, cu_q,
                                starts, B, N, nh, nkv, D, window, scale, max_q_len, splits, scratch, scratch_bytes,
-                               impl, chunk, sinks, gate, gate_stride, stream);
+                               impl, chunk, sinks, gate, gate_stride, keep, DV, out_table, out_pairing, positions,
+                               stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -519,5 +597,6 @@ EMS_EXPORT int ems_decode_attention_fused(const void* qkv, long long q_stride, v
     if (rc != EMS_OK || splits == 1) return rc;
     return launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)((size_t)B * nh)), dim3(D >= 128 ? 128 : 64), 0,
                       stream, (const float*)d.part_o, (const float*)d.part_ml, reinterpret_cast<bf16*>(out), splits, D,
-                      (const float*)nullptr, nh, (const bf16*)nullptr, 0LL);
+                      (const float*)nullptr, nh, (const bf16*)nullptr, 0LL, (const float*)nullptr, 0,
+                      (const int*)nullptr);
 }

@@ -24,14 +24,15 @@ namespace ems {
 
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                                 const int* __restrict__ deferred, float* __restrict__ residual, int H) {
+                                 const int* __restrict__ deferred, float* __restrict__ residual, int H,
+                                 float scale) {
     pdl_prologue();
     const size_t n = blockIdx.x;
     int tok = tokens[n];
     if (tok < 0) tok = deferred ? deferred[-(tok + 1)] : 0;
     const T* src = table + (size_t)tok * H;
     float* dst = residual + n * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32<T>(src[i]) * scale;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -305,15 +306,15 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int nh, int nkv, i
 using namespace ems;
 
 EMS_EXPORT int ems_embedding(const void* table, int dtype, const int* tokens, const int* deferred,
-                             float* residual, int N, int H, cudaStream_t stream) {
+                             float* residual, int N, int H, float scale, cudaStream_t stream) {
     if (N <= 0) return EMS_OK;
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == EMS_F32)
         return launch_pdl(embedding_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float*)table, tokens,
-                          deferred, residual, H);
+                          deferred, residual, H, scale);
     if (dtype == EMS_BF16)
         return launch_pdl(embedding_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (const bf16*)table, tokens,
-                          deferred, residual, H);
+                          deferred, residual, H, scale);
     return EMS_ERR_DTYPE;
 }
 

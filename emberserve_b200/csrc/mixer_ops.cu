@@ -44,18 +44,21 @@ __global__ void unary_act_vec_kernel(const uint4* __restrict__ x, uint4* __restr
     }
 }
 
-// One block per token, one warp per head at a time (query heads, then key heads).  proj row:
-// [q: nh*D | k: nkv*D | v: nkv*D (absent when the values are the keys)].  q is rewritten in place.
+// One block per token, one warp per head at a time (query heads, then key heads, then value heads).
+// proj row: [q: nh*D | k: nkv*D | v: nkv*DV (absent when the values are the keys)].  q is rewritten in
+// place.  A value head may be brought to unit RMS (v_normed) and turned by the token's position over its
+// whole length (v_table: [positions, DV / 2, (cos, sin)], pairs as v_pairing says) before it is cached.
 template <typename T>
 __global__ void qk_prep_kernel(T* __restrict__ proj, long long ld, int nh, int nkv, int D,
                                const int* __restrict__ positions, const int* __restrict__ row_of_token,
                                const float* __restrict__ table, int rot, int pairing, int normed, float eps,
                                T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ bt, int bt_stride,
-                               int page_size, int values_are_keys, int write_kv) {
+                               int page_size, int values_are_keys, int write_kv, int DV, int v_normed, float v_eps,
+                               const float* __restrict__ v_table, int v_pairing) {
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    float* buf = smem + (size_t)warp * D;
+    float* buf = smem + (size_t)warp * (D > DV ? D : DV);
     const int pos = positions[t];
     const int half = rot / 2;
     const float* cs = table ? table + (size_t)pos * half * 2 : nullptr;
@@ -65,16 +68,45 @@ __global__ void qk_prep_kernel(T* __restrict__ proj, long long ld, int nh, int n
         const int page = bt[(size_t)row_of_token[t] * bt_stride + pos / page_size];
         cache_at = ((size_t)page * nkv) * page_size + pos % page_size;  // + hk * page_size, times D below
     }
-    for (int h = warp; h < nh + nkv; h += nwarps) {
+    const int nvh = (values_are_keys || !write_kv) ? 0 : nkv;  // value heads that pass through this kernel
+    for (int h = warp; h < nh + nkv + nvh; h += nwarps) {
+        if (h >= nh + nkv) {  // a value head
+            const int hv = h - nh - nkv;
+            const T* src = rowp + (size_t)(nh + nkv) * D + (size_t)hv * DV;
+            T* dst = vc + (cache_at + (size_t)hv * page_size) * DV;
+            float ss = 0.f;
+            for (int d = lane; d < DV; d += 32) {
+                const float x = to_f32<T>(src[d]);
+                buf[d] = x;
+                ss = fmaf(x, x, ss);
+            }
+            const float r = v_normed ? rsqrtf(warp_sum(ss) / DV + v_eps) : 1.f;
+            __syncwarp();
+            if (v_table) {
+                const int vh = DV / 2;
+                const float* vcs = v_table + (size_t)pos * vh * 2;
+                for (int i = lane; i < vh; i += 32) {
+                    const int ia = v_pairing ? 2 * i : i, ib = v_pairing ? 2 * i + 1 : i + vh;
+                    const float c = vcs[2 * i], s = vcs[2 * i + 1];
+                    const float a = buf[ia] * r, b = buf[ib] * r;
+                    dst[ia] = from_f32<T>(a * c - b * s);
+                    dst[ib] = from_f32<T>(b * c + a * s);
+                }
+            } else {
+                for (int d = lane; d < DV; d += 32) dst[d] = v_normed ? from_f32<T>(buf[d] * r) : src[d];
+            }
+            __syncwarp();
+            continue;
+        }
         const bool is_k = h >= nh;
         const int hk = h - nh;
         T* src = rowp + (size_t)h * D;
         T* kdst = is_k && write_kv ? kc + (cache_at + (size_t)hk * page_size) * D : nullptr;
-        T* vdst = is_k && write_kv ? vc + (cache_at + (size_t)hk * page_size) * D : nullptr;
+        T* vdst = is_k && write_kv && values_are_keys ? vc + (cache_at + (size_t)hk * page_size) * D : nullptr;
         for (int d = lane; d < D; d += 32) {
             const T raw = src[d];
             buf[d] = to_f32<T>(raw);
-            if (vdst) vdst[d] = values_are_keys ? raw : rowp[(size_t)(nh + nkv + hk) * D + d];
+            if (vdst) vdst[d] = raw;
         }
         __syncwarp();
         if (cs) {
@@ -150,23 +182,29 @@ EMS_EXPORT int ems_unary_act(const void* x, void* out, int dtype, long long n, i
 EMS_EXPORT int ems_qk_prep(void* proj, long long ld, int dtype, int n, int nh, int nkv, int D, const int* positions,
                            const int* row_of_token, const float* table, int rot, int pairing, int normed, float eps,
                            void* kc, void* vc, const int* bt, int bt_stride, int page_size, int values_are_keys,
-                           int write_kv, cudaStream_t stream) {
+                           int write_kv, int DV, int v_normed, float v_eps, const float* v_table, int v_pairing,
+                           cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
+    if (DV <= 0) DV = D;
     if (D <= 0 || nh <= 0 || nkv <= 0 || rot < 0 || rot % 2 || rot > D || (rot > 0 && !table) ||
-        (write_kv && (!kc || !vc || !bt || page_size <= 0)))
+        (write_kv && (!kc || !vc || !bt || page_size <= 0)) || (values_are_keys && (DV != D || v_normed || v_table)) ||
+        (v_table && DV % 2))
         return EMS_ERR_SHAPE;
-    int warps = nh + nkv < 8 ? nh + nkv : 8;
-    const size_t smem = sizeof(float) * (size_t)warps * D;
+    const int heads = nh + nkv + (values_are_keys ? 0 : nkv);
+    int warps = heads < 8 ? heads : 8;
+    const size_t smem = sizeof(float) * (size_t)warps * (D > DV ? D : DV);
     if (smem > 48 * 1024) return EMS_ERR_SHAPE;
     const float* tab = rot > 0 ? table : nullptr;
     if (dtype == EMS_F32)
         qk_prep_kernel<float><<<n, warps * 32, smem, stream>>>((float*)proj, ld, nh, nkv, D, positions, row_of_token, tab,
                                                                rot, pairing, normed, eps, (float*)kc, (float*)vc, bt,
-                                                               bt_stride, page_size, values_are_keys, write_kv);
+                                                               bt_stride, page_size, values_are_keys, write_kv, DV,
+                                                               v_normed, v_eps, v_table, v_pairing);
     else if (dtype == EMS_BF16)
         qk_prep_kernel<bf16><<<n, warps * 32, smem, stream>>>((bf16*)proj, ld, nh, nkv, D, positions, row_of_token, tab,
                                                               rot, pairing, normed, eps, (bf16*)kc, (bf16*)vc, bt,
-                                                              bt_stride, page_size, values_are_keys, write_kv);
+                                                              bt_stride, page_size, values_are_keys, write_kv, DV,
+                                                              v_normed, v_eps, v_table, v_pairing);
     else
         return EMS_ERR_DTYPE;
     return launch_status();

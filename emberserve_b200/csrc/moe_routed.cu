@@ -5,7 +5,8 @@
 //   route     z[t, :] are the router's logits (32-bit, computed by the caller);
 //             s = softmax(z) over all experts; the `top` largest (ties: the lower index) are
 //             chosen; their weights are the scores s as they are (renorm = 0) or divided by
-//             their sum (renorm = 1).  The same kernel counts the pairs per expert, lays the
+//             their sum (renorm = 1).  With scoring = 1 the scores are sigmoid(z) instead, each
+//             expert by itself.  The same kernel counts the pairs per expert, lays the
 //             pairs out expert by expert (perm) and cuts each expert's rows into tiles.
 //   up        act[i, :] = f(x[token(i)] Wg[e]^T) * (x[token(i)] Wu[e]^T)   for sorted pair i of expert e
 //   down      y[pair(i), :] = act[i, :] Wd[e]^T            (32-bit, in pair order)
@@ -23,7 +24,8 @@ constexpr int MOE_TM = 64, MOE_TN = 64, MOE_TK = 16;
 // One warp chooses for one token: lane l holds the logits of experts l, l + 32, ... (up to 8 each,
 // so up to 256 experts; more are chosen by one lane alone).  Ties go to the lower index.
 __device__ __forceinline__ void moe_choose_serial(const float* __restrict__ z, int E, int top, int renorm,
-                                                  int* __restrict__ ids, float* __restrict__ wts, int* counts) {
+                                                  int* __restrict__ ids, float* __restrict__ wts, int* counts,
+                                                  int scoring) {
     float mx = -INFINITY;
     for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[e]);
     float sum = 0.f;
@@ -41,7 +43,7 @@ __device__ __forceinline__ void moe_choose_serial(const float* __restrict__ z, i
             }
         }
         ids[k] = best;
-        const float s = expf(bv - mx) / sum;
+        const float s = scoring ? 1.f / (1.f + expf(-bv)) : expf(bv - mx) / sum;
         wts[k] = s;
         chosen_sum += s;
         atomicAdd(&counts[best], 1);
@@ -51,10 +53,11 @@ __device__ __forceinline__ void moe_choose_serial(const float* __restrict__ z, i
 }
 
 __device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int E, int top, int renorm,
-                                                int* __restrict__ ids, float* __restrict__ wts, int* counts) {
+                                                int* __restrict__ ids, float* __restrict__ wts, int* counts,
+                                                int scoring) {
     const int lane = threadIdx.x & 31;
     if (E > 256) {
-        if (lane == 0) moe_choose_serial(z, E, top, renorm, ids, wts, counts);
+        if (lane == 0) moe_choose_serial(z, E, top, renorm, ids, wts, counts, scoring);
         return;
     }
     float v[8];
@@ -91,7 +94,7 @@ __device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int
                 bi = oi;
             }
         }
-        const float s = expf(bv - mx) / sum;
+        const float s = scoring ? 1.f / (1.f + expf(-bv)) : expf(bv - mx) / sum;
         chosen_sum += s;
         if (lane == 0) {
             ids[k] = bi;
@@ -111,7 +114,7 @@ __device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int
 // count of each tile.  One block.
 __global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ offsets,
-                                 int* __restrict__ perm, int* __restrict__ plan, int max_tiles) {
+                                 int* __restrict__ perm, int* __restrict__ plan, int max_tiles, int scoring) {
     extern __shared__ int sh[];
     int* counts = sh;       // [E]
     int* cursor = sh + E;   // [E]
@@ -119,7 +122,8 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E,
     for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     for (int t = threadIdx.x >> 5; t < n; t += blockDim.x >> 5)
-        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts);
+        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts,
+                        scoring);
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0, nt = 0;
@@ -150,10 +154,12 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E,
 // (counts in global memory, zeroed before), one block lays out offsets and tiles, one thread per
 // pair takes its place among its expert's rows.
 __global__ void moe_choose_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
-                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts) {
+                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
+                                  int scoring) {
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t < n)
-        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts);
+        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts,
+                        scoring);
 }
 
 // offsets: [E + 1]; counts and cursor: [E] each (the cursors are set to zero here).  With align > 1
@@ -212,6 +218,25 @@ __device__ __forceinline__ float moe_activation(float g, int act) {
     return g / (1.f + expf(-g));
 }
 
+// What the up product stores from the 32-bit sums cg (gate) and cu (up) of one output.  act 0..2:
+// f(g) * u of the two sums rounded to the storage type, as a product that is stored and read again would
+// be.  act 3, the capped form: with g = min(s * cg, limit) and u = clamp(s * cu, -limit, limit) it is
+// g * sigmoid(alpha * g) * (u + 1), all in 32 bits; s is the row's factor on the expert's INPUT (1 without).
+struct MoeAct {
+    int act;
+    float limit, alpha;
+};
+template <typename T>
+__device__ __forceinline__ float moe_glu(float cg, float cu, float s, const MoeAct a) {
+    if (a.act == 3) {
+        const float g = fminf(s * cg, a.limit);
+        const float u = fminf(fmaxf(s * cu, -a.limit), a.limit);
+        return g / (1.f + expf(-a.alpha * g)) * (u + 1.f);
+    }
+    const float g = round_to<T>(s * cg), u = round_to<T>(s * cu);
+    return moe_activation(g, a.act) * u;
+}
+
 // GLU = true:  A rows are x[perm[row] / top] (gathered), B = w[e] of shape [2 N, K]; the tile
 //              computes gate and up columns side by side and stores f(gate) * up in sorted order.
 // GLU = false: A rows are a[row] (sorted order), B = w[e] of shape [N, K]; the tile is stored at
@@ -219,8 +244,8 @@ __device__ __forceinline__ float moe_activation(float g, int act) {
 template <typename T, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* __restrict__ perm,
-                   const int* __restrict__ plan, int top, int N, int K, int act, T* __restrict__ out_t,
-                   float* __restrict__ out_f) {
+                   const int* __restrict__ plan, int top, int N, int K, const MoeAct act, T* __restrict__ out_t,
+                   float* __restrict__ out_f, const float* __restrict__ in_scale) {
     __shared__ float As[MOE_TK][MOE_TM + 4];
     __shared__ float Bs[MOE_TK][MOE_TN + 4];
     __shared__ float Bu[GLU ? MOE_TK : 1][MOE_TN + 4];
@@ -281,10 +306,8 @@ moe_grouped_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* 
             const int c = n0 + tx * 4 + j;
             if (c >= N) continue;
             if (GLU) {
-                // both projections are rounded to the storage type before the activation, as a
-                // product that is stored and read again would be
-                const float g = round_to<T>(cg[i][j]), u = round_to<T>(cu[i][j]);
-                out_t[(size_t)(row0 + r) * N + c] = from_f32<T>(moe_activation(g, act) * u);
+                const float sc = in_scale ? in_scale[perm[row0 + r]] : 1.f;
+                out_t[(size_t)(row0 + r) * N + c] = from_f32<T>(moe_glu<T>(cg[i][j], cu[i][j], sc, act));
             } else {
                 out_f[(size_t)perm[row0 + r] * N + c] = round_to<T>(cg[i][j]);
             }
@@ -322,8 +345,8 @@ __device__ __forceinline__ void mm_mma(float (&c)[4], const uint32_t (&a)[4], ui
 template <bool GLU>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const int* __restrict__ perm,
-                       const int* __restrict__ plan, int top, int N, int K, int act, bf16* __restrict__ out_t,
-                       float* __restrict__ out_f) {
+                       const int* __restrict__ plan, int top, int N, int K, const MoeAct act, bf16* __restrict__ out_t,
+                       float* __restrict__ out_f, const float* __restrict__ in_scale) {
     constexpr int LDS = MM_TK + MM_PAD;  // elements per shared-memory row
     extern __shared__ __align__(16) unsigned char mm_smem[];
     bf16* As = reinterpret_cast<bf16*>(mm_smem);      // [MM_STAGES][MM_TM][LDS]
@@ -417,15 +440,15 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, c
             const int r = wm * 32 + i * 16 + g + 8 * hrow;
             if (r >= rows) continue;
             if (GLU) {
+                const float sc = in_scale ? in_scale[perm[row0 + r]] : 1.f;
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int x = 0; x < 2; ++x) {
                         const int c = n0 + wn * 16 + nt * 8 + 2 * tq + x;
                         if (c >= N) continue;
-                        const float gv = round_to<bf16>(acc[i][nt][2 * hrow + x]);
-                        const float uv = round_to<bf16>(acc[i][2 + nt][2 * hrow + x]);
-                        out_t[(size_t)(row0 + r) * N + c] = from_f32<bf16>(moe_activation(gv, act) * uv);
+                        out_t[(size_t)(row0 + r) * N + c] = from_f32<bf16>(
+                            moe_glu<bf16>(acc[i][nt][2 * hrow + x], acc[i][2 + nt][2 * hrow + x], sc, act));
                     }
             } else {
                 float* dst = out_f + (size_t)perm[row0 + r] * N;
@@ -444,13 +467,16 @@ static bool moe_mma_ok(const void* a, const void* w, int K) {
     return K % 8 == 0 && !(reinterpret_cast<uintptr_t>(a) & 15) && !(reinterpret_cast<uintptr_t>(w) & 15);
 }
 
+// wts may be null (every weight 1: the scores went into the experts' inputs); `extra` (optional, [n, H]) is
+// added last: the output of an expert that every token uses.
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, T* __restrict__ out,
-                                   int top, int H) {
+                                   int top, int H, const T* __restrict__ extra) {
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s = fmaf(wts[t * top + k], y[(t * top + k) * H + c], s);
+        for (int k = 0; k < top; ++k) s = fmaf(wts ? wts[t * top + k] : 1.f, y[(t * top + k) * H + c], s);
+        if (extra) s += to_f32<T>(extra[t * H + c]);
         out[t * H + c] = from_f32<T>(s);
     }
 }
@@ -488,9 +514,9 @@ EMS_EXPORT int ems_moe_tile_rows() { return MOE_TM; }
 // sorted row of every pair.
 EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int renorm, int* ids, float* wts,
                              int* offsets, int* perm, int* plan, int max_tiles, int align, int* big, int max_big,
-                             int* inv, cudaStream_t stream) {
+                             int* inv, int scoring, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
-    if (top < 1 || top > E) return EMS_ERR_SHAPE;
+    if (top < 1 || top > E || scoring < 0 || scoring > 1) return EMS_ERR_SHAPE;
     if (align < 1 || (align > 1 && (n <= 512 || !big || max_big < n * top / align + (E < n * top ? E : n * top))))
         return EMS_ERR_SHAPE;
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
@@ -499,7 +525,7 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
         int* counts = offsets + E + 1;
         int* cursor = counts + E;
         if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream) != cudaSuccess) return EMS_ERR_LAUNCH;
-        moe_choose_kernel<<<(n + 7) / 8, 256, 0, stream>>>(logits, n, E, top, renorm, ids, wts, counts);
+        moe_choose_kernel<<<(n + 7) / 8, 256, 0, stream>>>(logits, n, E, top, renorm, ids, wts, counts, scoring);
         if (align > 1 &&
             cudaMemsetAsync(perm, 0xFF, (size_t)max_big * align * sizeof(int), stream) != cudaSuccess)
             return EMS_ERR_LAUNCH;
@@ -509,28 +535,34 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
         return launch_status();
     }
     int th = 32 * (n < 32 ? n : 32);  // a warp per token, up to 32 warps
-    moe_route_kernel<<<1, th, smem, stream>>>(logits, n, E, top, renorm, ids, wts, offsets, perm, plan, max_tiles);
+    moe_route_kernel<<<1, th, smem, stream>>>(logits, n, E, top, renorm, ids, wts, offsets, perm, plan, max_tiles,
+                                              scoring);
     return launch_status();
 }
 
+// act: 0 SiLU, 1 ReLU, 2 tanh-GELU, 3 the capped form (see MoeAct; `limit` and `alpha` are its constants);
+// in_scale (optional, [pairs] float): the factor on the input of each (token, choice) pair's expert.
 EMS_EXPORT int ems_moe_up(const void* x, const void* wgu, int dtype, const int* perm, const int* plan, int max_tiles,
-                          int top, int ff, int K, int act, void* out, int impl, cudaStream_t stream) {
+                          int top, int ff, int K, int act_code, void* out, int impl, const float* in_scale,
+                          float limit, float alpha, cudaStream_t stream) {
     if (max_tiles <= 0) return EMS_OK;
+    if (act_code < 0 || act_code > 3) return EMS_ERR_SHAPE;
+    const MoeAct act{act_code, limit, alpha};
     // impl: 0 the tensor-core kernel where it takes the case, 1 always the CUDA-core kernel
     if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(x, wgu, K)) {
         dim3 mg(max_tiles, (ff + MM_TB / 2 - 1) / (MM_TB / 2));
         cudaFuncSetAttribute(moe_grouped_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
         moe_grouped_mma_kernel<true><<<mg, 256, MM_SMEM, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top, ff, K,
-                                                             act, (bf16*)out, nullptr);
+                                                             act, (bf16*)out, nullptr, in_scale);
         return launch_status();
     }
     dim3 grid(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
     if (dtype == EMS_F32)
         moe_grouped_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)x, (const float*)wgu, perm, plan, top,
-                                                                  ff, K, act, (float*)out, nullptr);
+                                                                  ff, K, act, (float*)out, nullptr, in_scale);
     else if (dtype == EMS_BF16)
         moe_grouped_kernel<bf16, true><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top,
-                                                                 ff, K, act, (bf16*)out, nullptr);
+                                                                 ff, K, act, (bf16*)out, nullptr, in_scale);
     else
         return EMS_ERR_DTYPE;
     return launch_status();
@@ -543,16 +575,16 @@ EMS_EXPORT int ems_moe_down(const void* a, const void* wdown, int dtype, const i
         dim3 mg(max_tiles, (H + MM_TB - 1) / MM_TB);
         cudaFuncSetAttribute(moe_grouped_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
         moe_grouped_mma_kernel<false><<<mg, 256, MM_SMEM, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1, H, ff,
-                                                              0, nullptr, y);
+                                                              MoeAct{0, 0.f, 0.f}, nullptr, y, nullptr);
         return launch_status();
     }
     dim3 grid(max_tiles, (H + MOE_TN - 1) / MOE_TN);
     if (dtype == EMS_F32)
         moe_grouped_kernel<float, false><<<grid, 256, 0, stream>>>((const float*)a, (const float*)wdown, perm, plan, 1,
-                                                                   H, ff, 0, nullptr, y);
+                                                                   H, ff, MoeAct{0, 0.f, 0.f}, nullptr, y, nullptr);
     else if (dtype == EMS_BF16)
         moe_grouped_kernel<bf16, false><<<grid, 256, 0, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1,
-                                                                  H, ff, 0, nullptr, y);
+                                                                  H, ff, MoeAct{0, 0.f, 0.f}, nullptr, y, nullptr);
     else
         return EMS_ERR_DTYPE;
     return launch_status();
@@ -569,12 +601,12 @@ EMS_EXPORT int ems_moe_gather(const void* x, const int* perm, int rows, int top,
 }
 
 EMS_EXPORT int ems_moe_combine(const float* y, const float* wts, void* out, int dtype, int n, int top, int H,
-                               cudaStream_t stream) {
+                               const void* extra, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     int th = 32;
     while (th < H && th < 256) th <<= 1;
-    if (dtype == EMS_F32) moe_combine_kernel<float><<<n, th, 0, stream>>>(y, wts, (float*)out, top, H);
-    else if (dtype == EMS_BF16) moe_combine_kernel<bf16><<<n, th, 0, stream>>>(y, wts, (bf16*)out, top, H);
+    if (dtype == EMS_F32) moe_combine_kernel<float><<<n, th, 0, stream>>>(y, wts, (float*)out, top, H, (const float*)extra);
+    else if (dtype == EMS_BF16) moe_combine_kernel<bf16><<<n, th, 0, stream>>>(y, wts, (bf16*)out, top, H, (const bf16*)extra);
     else return EMS_ERR_DTYPE;
     return launch_status();
 }

@@ -229,7 +229,10 @@ __global__ void add_norm_grouped_vec_kernel(const T* __restrict__ delta, const v
 }
 
 // ---------------------------------------------------------------------------------------
-// out[n, i] = act(gu[n, i]) * gu[n, I + i];  act: 0 SiLU, 1 ReLU, 2 GELU (tanh form)
+// out[n, i] = act(gu[n, i]) * gu[n, I + i];  act: 0 SiLU, 1 ReLU, 2 GELU (tanh form); 3 the capped form:
+// with g = min(gate, limit) and u = clamp(up, -limit, limit) it is g * sigmoid(alpha * g) * (u + 1).
+// A row of gu has `ld` elements; with row_gate, column 2 I of the row holds a number z and the whole
+// output row is multiplied by sigmoid(z).
 
 __device__ __forceinline__ float glu_activation(float g, int act) {
     if (act == 1) return fmaxf(g, 0.f);
@@ -238,12 +241,23 @@ __device__ __forceinline__ float glu_activation(float g, int act) {
 }
 
 template <typename T>
-__global__ void glu_act_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int act) {
+__global__ void glu_act_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, int I, int act,
+                               float limit, float alpha, int row_gate) {
     const size_t n = blockIdx.x;
-    const T* g = gu + n * 2 * I;
+    const T* g = gu + n * ld;
     T* o = out + n * I;
-    for (int i = threadIdx.x; i < I; i += blockDim.x)
-        o[i] = from_f32<T>(glu_activation(to_f32<T>(g[i]), act) * to_f32<T>(g[I + i]));
+    const float rg = row_gate ? 1.f / (1.f + expf(-to_f32<T>(g[2 * I]))) : 1.f;
+    for (int i = threadIdx.x; i < I; i += blockDim.x) {
+        float gv = to_f32<T>(g[i]), uv = to_f32<T>(g[I + i]), y;
+        if (act == 3) {
+            gv = fminf(gv, limit);
+            uv = fminf(fmaxf(uv, -limit), limit);
+            y = gv / (1.f + expf(-alpha * gv)) * (uv + 1.f);
+        } else {
+            y = glu_activation(gv, act) * uv;
+        }
+        o[i] = from_f32<T>(y * rg);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -396,12 +410,15 @@ EMS_EXPORT int ems_add_norm_grouped(const void* delta, const void* post_gain, in
     return launch_status();
 }
 
-EMS_EXPORT int ems_glu_act(const void* gu, void* out, int dtype, int n, int I, int act, cudaStream_t stream) {
+EMS_EXPORT int ems_glu_act(const void* gu, long long ld, void* out, int dtype, int n, int I, int act, float limit,
+                           float alpha, int row_gate, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
-    if (act < 0 || act > 2) return EMS_ERR_SHAPE;
+    if (act < 0 || act > 3 || ld < 2 * I + (row_gate ? 1 : 0)) return EMS_ERR_SHAPE;
     const int th = threads_for(I);
-    if (dtype == EMS_F32) glu_act_kernel<float><<<n, th, 0, stream>>>((const float*)gu, (float*)out, I, act);
-    else if (dtype == EMS_BF16) glu_act_kernel<bf16><<<n, th, 0, stream>>>((const bf16*)gu, (bf16*)out, I, act);
+    if (dtype == EMS_F32)
+        glu_act_kernel<float><<<n, th, 0, stream>>>((const float*)gu, ld, (float*)out, I, act, limit, alpha, row_gate);
+    else if (dtype == EMS_BF16)
+        glu_act_kernel<bf16><<<n, th, 0, stream>>>((const bf16*)gu, ld, (bf16*)out, I, act, limit, alpha, row_gate);
     else return EMS_ERR_DTYPE;
     return launch_status();
 }

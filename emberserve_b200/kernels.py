@@ -57,7 +57,7 @@ def library_path() -> str:
 def _declare(lib: ctypes.CDLL) -> None:
     P, I, L, F = c_void_p, c_int, c_longlong, c_float
     sigs = {
-        "ems_embedding": [P, I, P, P, P, I, I, P],
+        "ems_embedding": [P, I, P, P, P, I, I, F, P],
         "ems_add_rmsnorm": [P, P, P, I, P, I, P, I, I, F, I, P],
         "ems_silu_mul": [P, P, I, I, I, P],
         "ems_rope_table": [P, P, I, I, P],
@@ -74,12 +74,12 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_gemm_large_gated": [P, P, P, I, I, I, I, P],
         "ems_stream_inject": [P, P, P, P, P, I, I, I, P],
         "ems_add_norm_grouped": [P, P, I, I, F, P, P, I, I, F, P, I, P, I, I, I, P],
-        "ems_glu_act": [P, P, I, I, I, I, P],
+        "ems_glu_act": [P, L, P, I, I, I, I, F, F, I, P],
         "ems_causal_taps": [P, L, P, I, P, I, P, P, P, P, P, I, I, I, I, I, P],
         "ems_paged_attention_masked": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, I, P, P, L, F, I, I,
-                                       P, L, I, P],
+                                       P, L, I, I, I, P, I, P, P],
         "ems_unary_act": [P, P, I, L, I, P],
-        "ems_qk_prep": [P, L, I, I, I, I, I, P, P, P, I, I, I, F, P, P, P, I, I, I, I, P],
+        "ems_qk_prep": [P, L, I, I, I, I, I, P, P, P, I, I, I, F, P, P, P, I, I, I, I, I, I, F, P, I, P],
         "ems_norm_mean2": [P, P, P, P, I, P, I, I, I, F, P],
         "ems_matrix_recurrence": [P, L, P, L, P, L, I, I, F, P, P, P, P, F, P, P, I, I, P, P, I, I, I, I, I, P, P],
         "ems_mlstm_gates": [P, P, P, I, F, P, I, I, P, P, I, I, P, P, P, P],
@@ -89,14 +89,17 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_rope_inplace": [P, I, I, I, I, I, I, I, I, P, P, P],
         "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, I, P],
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
-        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P, P],
+        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P, I, P],
         "ems_moe_down_grouped_tc05": [P, P, P, I, I, I, I, P, P],
         "ems_moe_combine_rows": [P, P, P, P, I, I, I, P],
         "ems_moe_gather": [P, P, I, I, I, P, P],
         "ems_moe_up_grouped_tc05": [P, P, P, I, I, I, I, P, P],
-        "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P],
+        "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P, F, F, P],
         "ems_moe_down": [P, P, I, P, P, I, I, I, P, I, P],
-        "ems_moe_combine": [P, P, P, I, I, I, I, P],
+        "ems_moe_combine": [P, P, P, I, I, I, I, P, P],
+        "ems_add_cast": [P, P, P, I, I, I, P],
+        "ems_token_gate": [P, P, I, L, I, P, P, P, I, I, I, P],
+        "ems_depth_mix": [P, P, I, F, P, P, P, I, L, I, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -212,14 +215,14 @@ def record_event() -> "torch.cuda.Event":
 
 
 def embedding(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor,
-              deferred: torch.Tensor | None = None) -> None:
-    """residual[n, :] = float32(table[tokens[n], :]); a token -(k + 1) reads deferred[k] (a token
+              deferred: torch.Tensor | None = None, scale: float = 1.0) -> None:
+    """residual[n, :] = float32(table[tokens[n], :]) * scale; a token -(k + 1) reads deferred[k] (a token
     sampled on the device by an earlier kernel of the stream)."""
     n, h = residual.shape
     assert table.shape[1] == h and residual.dtype == torch.float32 and tokens.numel() >= n
     _check(library().ems_embedding(_ptr(table, "table"), _dt(table), _i32(tokens, "tokens"),
                                    None if deferred is None else _i32(deferred, "deferred"),
-                                   _ptr(residual, "residual"), n, h, _stream()), "embedding")
+                                   _ptr(residual, "residual"), n, h, float(scale), _stream()), "embedding")
 
 
 def add_rmsnorm(delta: torch.Tensor | None, residual: torch.Tensor, weight: torch.Tensor,
@@ -322,15 +325,60 @@ def add_norm_grouped(delta: torch.Tensor | None, post_gain: torch.Tensor | None,
         _dt(out), _i32(rows, "rows"), n_out, h, 0 if rows is not None else 1, _stream()), "add_norm_grouped")
 
 
-GLU_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+# "swiglu_capped": with g = min(gate, limit) and u = clamp(up, -limit, limit) the result is
+# g * sigmoid(alpha * g) * (u + 1); the other three are act(gate) * up.
+GLU_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "swiglu_capped": 3}
 
 
-def glu_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> None:
-    """out[n, i] = act(gate_up[n, i]) * gate_up[n, I + i] for act in `GLU_ACTIVATIONS`."""
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, act: str, limit: float = 0.0, alpha: float = 1.0,
+            row_gate: bool = False) -> None:
+    """out[n, i] = act(gate_up[n, i]) * gate_up[n, I + i] for act in `GLU_ACTIVATIONS` (`limit` and `alpha`
+    are the constants of "swiglu_capped").  gate_up may have more columns than 2 I; with `row_gate`,
+    column 2 I holds a number z per row and the row of `out` is multiplied by sigmoid(z)."""
     n, i = out.shape
-    assert gate_up.shape == (n, 2 * i) and gate_up.dtype == out.dtype
-    _check(library().ems_glu_act(_ptr(gate_up, "gate_up"), _ptr(out, "out"), _dt(out), n, i,
-                                 GLU_ACTIVATIONS[act], _stream()), "glu_act")
+    assert gate_up.shape[0] == n and gate_up.shape[1] >= 2 * i + (1 if row_gate else 0)
+    assert gate_up.dtype == out.dtype and gate_up.is_contiguous()
+    _check(library().ems_glu_act(_ptr(gate_up, "gate_up"), gate_up.shape[1], _ptr(out, "out"), _dt(out), n, i,
+                                 GLU_ACTIVATIONS[act], float(limit), float(alpha), 1 if row_gate else 0, _stream()),
+           "glu_act")
+
+
+def add_cast(delta: torch.Tensor | None, residual: torch.Tensor, out: torch.Tensor) -> None:
+    """residual += delta (32-bit; delta may be None); out = residual rounded to out's type: the stream
+    itself as the operand of a product."""
+    n, h = residual.shape
+    assert residual.dtype == torch.float32 and out.shape == (n, h)
+    assert delta is None or (delta.dtype == out.dtype and delta.shape[-1] == h and delta.shape[0] >= n)
+    _check(library().ems_add_cast(_ptr(delta, "delta"), _ptr(residual, "residual"), _ptr(out, "out"), _dt(out), n, h,
+                                  _stream()), "add_cast")
+
+
+def token_gate(z: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor,
+               deferred: torch.Tensor | None = None) -> None:
+    """out[n, :] = gelu_tanh(z[n, :]) * table[tokens[n], col0 : col0 + C] (32-bit, rounded once); a token
+    -(k + 1) reads deferred[k], as in `embedding`."""
+    n, c = z.shape
+    assert out.shape == (n, c) and z.dtype == out.dtype and table.dim() == 2 and tokens.numel() >= n
+    _check(library().ems_token_gate(_ptr(z, "z"), _ptr(table, "table"), _dt(table), table.shape[1], int(col0),
+                                    _i32(tokens, "tokens"), None if deferred is None else _i32(deferred, "deferred"),
+                                    _ptr(out, "out"), _dt(out), n, c, _stream()), "token_gate")
+
+
+def depth_mix(delta: torch.Tensor | None, gain: torch.Tensor | None, eps: float, residual: torch.Tensor,
+              hist: torch.Tensor, weights: torch.Tensor | None, count: int) -> None:
+    """The newest state of the stream, x = residual + delta (delta / sqrt(mean(delta^2) + eps) * gain when
+    a gain is given; delta may be None), is stored as hist[count - 1]; the residual becomes
+    sum_j weights[j] * hist[j] over j < count (it stays x when `weights` is None).  hist: [depths, N, H]
+    float32; all of it 32-bit."""
+    n, h = residual.shape
+    assert residual.dtype == hist.dtype == torch.float32 and hist.shape[1:] == (n, h) and 1 <= count <= hist.shape[0]
+    assert delta is None or (delta.shape[-1] == h and delta.shape[0] >= n)
+    assert weights is None or (weights.dtype == torch.float32 and weights.numel() >= count)
+    assert gain is None or (delta is not None and gain.numel() == h)
+    dt = _dt(delta) if delta is not None else 0
+    _check(library().ems_depth_mix(_ptr(delta, "delta"), _ptr(gain, "gain"), 0 if gain is None else _dt(gain),
+                                   float(eps), _ptr(residual, "residual"), _ptr(hist, "hist"),
+                                   _ptr(weights, "weights"), count, n * h, dt, n, h, _stream()), "depth_mix")
 
 
 def causal_taps(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, slots: torch.Tensor | None,
@@ -446,12 +494,15 @@ def moe_max_tiles(num_pairs: int, num_experts: int, tile_rows: int) -> int:
 
 
 MOE_BIG_TILE_ROWS = 256  # rows of a tile of the tcgen05 grouped product
+MOE_SCORINGS = {"softmax": 0, "sigmoid": 1}
 
 
 def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
               offsets: torch.Tensor, perm: torch.Tensor, plan: torch.Tensor, max_tiles: int,
-              align: int = 1, big: torch.Tensor | None = None, inv: torch.Tensor | None = None) -> None:
-    """From router logits [N, E] (float32): softmax over all experts, the `top` largest per token
+              align: int = 1, big: torch.Tensor | None = None, inv: torch.Tensor | None = None,
+              scoring: str = "softmax") -> None:
+    """From router logits [N, E] (float32): softmax over all experts (or, with scoring "sigmoid", the
+    sigmoid of every logit by itself), the `top` largest per token
     (ids, weights: [N, top]; the weights are the scores, divided by their sum if `renormalize`),
     the first sorted row of every expert (offsets [E + 1], in a buffer of 3 E + 1: counters follow),
     the pairs t * top + k in expert order
@@ -469,7 +520,7 @@ def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tens
     _check(library().ems_moe_route(_ptr(logits, "logits"), n, e, top, 1 if renormalize else 0, _i32(ids, "ids"),
                                    _ptr(weights, "weights"), _i32(offsets, "offsets"), _i32(perm, "perm"),
                                    _i32(plan, "plan"), max_tiles, align, _i32(big, "big"), max_big,
-                                   _i32(inv, "inv"), _stream()),
+                                   _i32(inv, "inv"), MOE_SCORINGS[scoring], _stream()),
            "moe_route", 1 if n <= 512 else 4)
 
 
@@ -499,15 +550,19 @@ def moe_up_grouped_tc05(xs: torch.Tensor, wgu: torch.Tensor, big: torch.Tensor, 
 
 
 def moe_up(x: torch.Tensor, wgu: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
-           max_tiles: int, top: int, act: str, out: torch.Tensor, kernel: str = "auto") -> None:
+           max_tiles: int, top: int, act: str, out: torch.Tensor, kernel: str = "auto",
+           in_scale: torch.Tensor | None = None, limit: float = 0.0, alpha: float = 1.0) -> None:
     """out[i, :] = act(x[t] Wg[e]^T) * (x[t] Wu[e]^T) for sorted pair i (token t = perm[i] // top) of
     expert e; wgu: [E, 2 * ff, K] with the gate rows first.  bfloat16 runs on the tensor cores where K
-    is a multiple of 8; kernel="generic" keeps the CUDA-core kernel."""
+    is a multiple of 8; kernel="generic" keeps the CUDA-core kernel.  With `in_scale` (float32, one
+    number per pair) the expert reads in_scale[pair] * x[t]: both 32-bit sums are multiplied by it.
+    `limit` and `alpha` are the constants of the activation "swiglu_capped"."""
     e, ff2, k = wgu.shape
     assert x.shape[1] == k and out.shape[1] * 2 == ff2 and x.dtype == wgu.dtype == out.dtype
     _check(library().ems_moe_up(_ptr(x, "x"), _ptr(wgu, "wgu"), _dt(x), _i32(perm, "perm"), _i32(plan, "plan"),
                                 max_tiles, top, ff2 // 2, k, GLU_ACTIVATIONS[act], _ptr(out, "out"),
-                                1 if kernel == "generic" else 0, _stream()), "moe_up")
+                                1 if kernel == "generic" else 0, _f32(in_scale, "in_scale"), float(limit),
+                                float(alpha), _stream()), "moe_up")
 
 
 def moe_down(act: torch.Tensor, wdown: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
@@ -541,12 +596,15 @@ def moe_combine_rows(y: torch.Tensor, inv: torch.Tensor, weights: torch.Tensor, 
                                           n, top, h, _stream()), "moe_combine_rows")
 
 
-def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> None:
-    """out[t, :] = sum_k weights[t, k] * y[t * top + k, :], k ascending."""
+def moe_combine(y: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor, top: int,
+                extra: torch.Tensor | None = None) -> None:
+    """out[t, :] = sum_k weights[t, k] * y[t * top + k, :] (k ascending; every weight 1 when `weights` is
+    None) + extra[t, :] (optional, of out's type)."""
     n, h = out.shape
-    assert y.dtype == torch.float32 and weights.dtype == torch.float32 and y.shape[1] == h
+    assert y.dtype == torch.float32 and y.shape[1] == h and (weights is None or weights.dtype == torch.float32)
+    assert extra is None or (extra.dtype == out.dtype and extra.shape == out.shape)
     _check(library().ems_moe_combine(_ptr(y, "y"), _ptr(weights, "weights"), _ptr(out, "out"), _dt(out), n, top, h,
-                                     _stream()), "moe_combine")
+                                     _ptr(extra, "extra"), _stream()), "moe_combine")
 
 
 def attention_scratch_bytes(num_tokens: int, num_heads: int, head_dim: int, splits: int) -> int:
@@ -628,17 +686,23 @@ def unary_act(x: torch.Tensor, out: torch.Tensor, act: str) -> None:
 def qk_prep(proj: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
             row_of_token: torch.Tensor, table: torch.Tensor | None, rot_dims: int, pairing: str,
             norm_eps: float | None, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
-            values_are_keys: bool, write: bool = True) -> None:
+            values_are_keys: bool, write: bool = True, v_norm_eps: float | None = None,
+            v_table: torch.Tensor | None = None, v_pairing: str = "half") -> None:
     """The tokens of a step for attention over a paged cache.  proj: [N, >= (nh + nkv (+ nkv)) * D]
     holds [q | k | v] per row (no v when `values_are_keys`: the value of a token is then its key as
     projected).  Every head of q and k is rotated by the table rows of `positions` on its first
     `rot_dims` numbers and, with `norm_eps`, divided by its root mean square; q is rewritten in
-    place, k and v go to the token's page slot.  caches: [pages, nkv, page_size, D]."""
+    place, k and v go to the token's page slot.  caches: [pages, nkv, page_size, D]; the value cache may
+    have another last dimension DV (the v columns of `proj` are then nkv * DV wide).  With `v_norm_eps`
+    every value head is divided by its root mean square, and with `v_table` ([positions, DV / 2, 2]) it
+    is turned by the token's position over its whole length, before it is cached."""
     n = proj.shape[0]
-    cols = (num_heads + num_kv_heads * (1 if values_are_keys else 2)) * head_dim
+    dv = vcache.shape[3]
+    cols = (num_heads + num_kv_heads) * head_dim + (0 if values_are_keys else num_kv_heads * dv)
     assert proj.stride(1) == 1 and proj.shape[1] >= cols
     assert kcache.dtype == vcache.dtype == proj.dtype and kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim
     assert table is None or (table.dtype == torch.float32 and table.shape[1] * 2 == rot_dims)
+    assert v_table is None or (v_table.dtype == torch.float32 and v_table.shape[1] * 2 == dv)
     if not proj.is_cuda:
         raise KernelError("proj must be a CUDA tensor (emberserve_b200 has no CPU path)")
     _check(library().ems_qk_prep(
@@ -646,7 +710,9 @@ def qk_prep(proj: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int
         _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _ptr(table, "table"),
         rot_dims if table is not None else 0, ROTARY_PAIRINGS[pairing], 0 if norm_eps is None else 1,
         float(norm_eps or 0.0), _ptr(kcache, "kcache"), _ptr(vcache, "vcache"), _i32(block_tables, "block_tables"),
-        block_tables.shape[1], kcache.shape[2], 1 if values_are_keys else 0, 1 if write else 0, _stream()), "qk_prep")
+        block_tables.shape[1], kcache.shape[2], 1 if values_are_keys else 0, 1 if write else 0, dv,
+        0 if v_norm_eps is None else 1, float(v_norm_eps or 0.0), _ptr(v_table, "v_table"),
+        ROTARY_PAIRINGS[v_pairing], _stream()), "qk_prep")
 
 
 def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -655,15 +721,24 @@ def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Ten
                            head_dim: int, scale: float, max_q_len: int, window: int | None = None,
                            chunk: int | None = None, sinks: torch.Tensor | None = None,
                            gate: torch.Tensor | None = None, splits: int = 1,
-                           scratch: torch.Tensor | None = None, kernel: str = "auto") -> None:
+                           scratch: torch.Tensor | None = None, kernel: str = "auto", keep_first: int = 0,
+                           out_table: torch.Tensor | None = None, out_pairing: str = "half",
+                           positions: torch.Tensor | None = None) -> None:
     """`paged_attention` with three optional extras: `chunk` (the query at position p sees key j <= p
     only if j // chunk == p // chunk, chunks counted from position 0 of the request), `sinks`
     (float32 [nh]: exp(sinks[h]) is added to head h's softmax denominator; it has no value) and
     `gate` ([N, >= nh], may be a column range of a wider buffer: head h's output is multiplied by
-    sigmoid(gate[n, h]))."""
+    sigmoid(gate[n, h])).  Further: `keep_first` (keys j < keep_first stay visible to every later query
+    beside the window or chunk); a value cache whose last dimension DV differs from head_dim (out is
+    then [N, nh * DV]); `out_table` ([positions, DV / 2, 2]: the values were turned by their positions
+    when they were cached, and each head's result is turned back by the query's position, positions[n]
+    of token n)."""
     assert q.stride(1) == 1 and out.is_contiguous() and q.dtype == out.dtype == kcache.dtype
     page_size = kcache.shape[2]
-    assert kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim
+    dv = vcache.shape[3]
+    assert kcache.shape[1] == num_kv_heads and kcache.shape[3] == head_dim and out.shape[1] == num_heads * dv
+    assert out_table is None or (out_table.dtype == torch.float32 and out_table.shape[1] * 2 == dv
+                                 and positions is not None)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads)
     assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[1] >= num_heads)
     if not q.is_cuda:
@@ -675,7 +750,9 @@ def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Ten
         head_dim, int(window or 0), int(chunk or 0), _ptr(sinks, "sinks"),
         None if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0), float(scale), max_q_len,
         splits, _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
-        _ATTENTION_IMPL[kernel], _stream()), "paged_attention_masked", 2 if splits > 1 else 1)
+        _ATTENTION_IMPL[kernel], int(keep_first or 0), dv, _ptr(out_table, "out_table"),
+        ROTARY_PAIRINGS[out_pairing], None if positions is None else _i32(positions, "positions"), _stream()),
+        "paged_attention_masked", 2 if splits > 1 else 1)
 
 
 def norm_mean2(a: torch.Tensor, b: torch.Tensor, gain_a: torch.Tensor, gain_b: torch.Tensor, eps: float,

@@ -59,17 +59,26 @@ class PagedKV:
     """Keys and values of every token, in pages.  `window`: only the last `window`
     keys are ever read again (None = all), so older pages may be given back.  `chunk`: a query
     reads only keys of its own chunk of `chunk` positions (chunks counted from position 0), so
-    pages that lie wholly before the chunk of the next position may be given back."""
+    pages that lie wholly before the chunk of the next position may be given back.  `keep_first`:
+    the keys of positions below it are read by every later query whatever window or chunk say, so
+    the pages that hold them are never given back.  `v_head_dim`: numbers per value head where
+    they differ from the key heads' (None = head_dim)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     chunk: int | None = None
+    keep_first: int = 0
+    v_head_dim: int | None = None
 
     paged = True
 
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
     def elements_per_token(self) -> int:
-        return 2 * self.num_kv_heads * self.head_dim
+        return self.num_kv_heads * (self.head_dim + self.value_dim)
 
 
 @dataclass(frozen=True)
@@ -105,12 +114,13 @@ class PagedKVHandle:
     """One cache entry of kind PagedKV as a mixer sees it during a step."""
 
     k: torch.Tensor  # [num_pages, num_kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor  # [num_pages, num_kv_heads, page_size, value_dim]
     block_tables: torch.Tensor  # [rows, max_pages] int32, page ids of this entry's group
     page_size: int
     window: int | None
     write: bool  # False: read what another layer call wrote in this step
     chunk: int | None = None
+    keep_first: int = 0
 
 
 @dataclass
@@ -345,6 +355,22 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamPart(Part):
+    """Something that acts on the residual stream itself, behind a layer's sub-layers (a block lists
+    such parts in its spec and runs them in order): an input of the layer's own that is added to the
+    stream, a mix of the stream's states at several depths."""
+
+    def on_entry(self, residual: torch.Tensor, ctx: StepContext) -> None:
+        """Called before the block's first sub-layer, with the stream as the block receives it."""
+        return None
+
+    def forward(self, delta: Any, residual: torch.Tensor, ctx: StepContext) -> Any:
+        """`delta` is what the block's last sub-layer (or the stream part before this one) left to be
+        added to the stream: None, a tensor or a `NormedDelta`.  Returns what is still to be added
+        (None once everything is in `residual`)."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of a mixer, a feed-forward and their norms.  Works on the pair
     (delta, residual): `delta` is the previous sub-layer's output that has not been
@@ -371,13 +397,13 @@ class Block(Part):
 # ---------------------------------------------------------------------------------------
 # registries: spec kind -> part class
 
-_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "conv")
+_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "conv", "stream")
 _REGISTRY: dict[str, dict[str, type[Part]]] = {c: {} for c in _CATEGORIES}
 
 
 def register_part(category: str, kind: str, cls: type[Part] | None = None):
     """Register `cls` as the part built for specs of `kind` in `category` (one of
-    mixer, feed_forward, norm, position, block, conv).  Usable as a decorator."""
+    mixer, feed_forward, norm, position, block, conv, stream).  Usable as a decorator."""
     if category not in _REGISTRY:
         raise KeyError(f"unknown part category {category!r}; one of {_CATEGORIES}")
 

@@ -1,6 +1,7 @@
 """Residual blocks.
 
-Pre-norm: ``h += mixer(norm1(h)); h += ffn(norm2(h))`` (a layer without a feed-forward is its first half).
+Pre-norm: ``h += mixer(norm1(h)); h += ffn(norm2(h))`` (a layer without a feed-forward is its first half);
+behind the sub-layers a block may run parts that act on the stream itself (``stream_parts``, in order).
 Sandwich (a norm before AND behind every sub-layer, optionally a short convolution before the
 mixer, optionally no feed-forward): ``h += norm1b(mixer(conv(norm1(h)))); h += norm2b(ffn(norm2(h)))``.
 
@@ -16,7 +17,7 @@ from typing import Any
 
 import torch
 
-from emberserve_b200.parts.base import (Block, CacheNeed, NormedDelta, Part, StepContext, build_part,
+from emberserve_b200.parts.base import (Block, CacheNeed, NormedDelta, Part, StepContext, StreamPart, build_part,
                                         register_part)
 
 
@@ -27,6 +28,7 @@ class PreNormBlockSpec:
     mixer_norm: Any
     ffn_norm: Any
     kind: str = "prenorm"
+    stream_parts: tuple = ()  # specs of category "stream", run in order behind the sub-layers
 
 
 @register_part("block", "prenorm")
@@ -39,11 +41,15 @@ class PreNormBlock(Block):
         if spec.feed_forward is not None:
             self.ffn_norm = build_part("norm", spec.ffn_norm, prefix + ".ffn_norm", self.shared)
             self.ffn = build_part("feed_forward", spec.feed_forward, prefix + ".ffn", self.shared)
+        self.stream_parts = [build_part("stream", sp, f"{prefix}.stream{j}", self.shared)
+                             for j, sp in enumerate(spec.stream_parts)]
 
     def children(self) -> dict[str, Part]:
         out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
         if self.ffn is not None:
             out.update(ffn_norm=self.ffn_norm, ffn=self.ffn)
+        for j, part in enumerate(self.stream_parts):
+            out[f"stream{j}"] = part
         return out
 
     def cache_need(self) -> CacheNeed | None:
@@ -54,6 +60,21 @@ class PreNormBlock(Block):
 
     def forward(self, delta: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
                 cache: Any) -> torch.Tensor:
+        if not self.stream_parts:
+            return self._sublayers(delta, residual, ctx, cache)
+        ctx.extra["next_norm"] = None  # (the stream parts stand between this block's last product and that norm)
+        if delta is not None and any(type(p).on_entry is not StreamPart.on_entry for p in self.stream_parts):
+            raise TypeError(f"{self.prefix}: its stream parts read the stream on entry, so the block before "
+                            f"must leave nothing to be added")
+        for part in self.stream_parts:
+            part.on_entry(residual, ctx)
+        delta = self._sublayers(delta, residual, ctx, cache)
+        for part in self.stream_parts:
+            delta = part.forward(delta, residual, ctx)
+        return delta
+
+    def _sublayers(self, delta: torch.Tensor | None, residual: torch.Tensor, ctx: StepContext,
+                   cache: Any) -> torch.Tensor:
         # A sub-layer whose successor takes `ScaledRows` is asked to begin the norm that follows
         # it in its last product (ctx.extra["norm_behind"]); what it returns says whether it did.
         after_ffn = ctx.extra.pop("next_norm", None)  # the next block's entry norm, from the decoder

@@ -62,6 +62,7 @@ class DecoderSpec:
     # Tables of vectors that belong to the decoder itself: local name -> (checkpoint tensor, rows);
     # each is [rows, hidden].  `StreamInject` names them.
     tables: dict[str, tuple[str, int]] = field(default_factory=dict)
+    embed_scale: float = 1.0  # the embedding row is multiplied by this as it enters the 32-bit stream
 
 
 class Decoder:
@@ -203,7 +204,7 @@ class Decoder:
         s = self.spec
         n = ctx.num_tokens
         residual = ctx.scratch("residual", (n, s.hidden), torch.float32)
-        K.embedding(self.embed, ctx.tokens, residual, deferred=ctx.deferred)
+        K.embedding(self.embed, ctx.tokens, residual, deferred=ctx.deferred, scale=s.embed_scale)
         if self.embed_position is not None:
             self.embed_position.on_embedding(residual, ctx)
         delta = None

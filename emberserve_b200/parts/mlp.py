@@ -1,5 +1,8 @@
 """Dense feed-forwards.  Gated: ``down(act(gate(x)) * up(x))``, no biases; act is SiLU (SwiGLU)
-unless the spec names another (``relu``, ``gelu_tanh``), which takes the unfused kernels.
+unless the spec names another (``relu``, ``gelu_tanh``, ``swiglu_capped``: see
+``kernels.GLU_ACTIVATIONS``), which takes the unfused kernels.  With `token_gate_name` ([1, hidden]) the
+output of every token is multiplied by ``sigmoid(x . wg)``: the gate is one more column of the gate/up
+product and is applied to the activation (one number per row passes the down projection unchanged).
 Ungated (``DenseMLP``): ``down(act(up(x)))`` with act one of ``kernels.UNARY_ACTIVATIONS``
 (``relu2`` is the square of relu).
 
@@ -30,6 +33,9 @@ class SwiGLUSpec:
     kind: str = "swiglu"
     activation: str = "silu"  # one of kernels.GLU_ACTIVATIONS
     weight_suffix: str = ".weight"  # what follows the three names in the checkpoint
+    act_limit: float = 0.0  # the two constants of "swiglu_capped"
+    act_alpha: float = 1.0
+    token_gate_name: str | None = None  # full name of a [1, hidden] tensor: the output times sigmoid(x . wg)
 
 
 @register_part("feed_forward", "swiglu")
@@ -46,9 +52,13 @@ class SwiGLU(FeedForward):
     def param_specs(self) -> dict[str, ParamSpec]:
         s: SwiGLUSpec = self.spec
         i = s.intermediate
+        srcs = [Source(s.gate_name + s.weight_suffix, (0, i)), Source(s.up_name + s.weight_suffix, (i, 2 * i))]
+        rows = 2 * i
+        if s.token_gate_name is not None:  # (padded so that a row of the product stays 16-byte aligned)
+            srcs.append(Source(s.token_gate_name, (2 * i, 2 * i + 1)))
+            rows = 2 * i + 8
         return {
-            "wgu": ParamSpec((2 * i, s.hidden), [Source(s.gate_name + s.weight_suffix, (0, i)),
-                                                 Source(s.up_name + s.weight_suffix, (i, 2 * i))]),
+            "wgu": ParamSpec((rows, s.hidden), srcs),
             "wdown": ParamSpec((s.hidden, i), [Source(s.down_name + s.weight_suffix)]),
         }
 
@@ -57,16 +67,17 @@ class SwiGLU(FeedForward):
 
     def scratch_elements_per_token(self) -> int:
         # ffn_act, ffn_out, and gate_up for the steps in which no fused kernel takes the sizes
-        return 3 * self.spec.intermediate + self.spec.hidden
+        return 3 * self.spec.intermediate + self.spec.hidden + (8 if self.spec.token_gate_name is not None else 0)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s: SwiGLUSpec = self.spec
         n = x.shape[0]
         act = ctx.scratch("ffn_act", (n, s.intermediate), ctx.dtype)
-        if s.activation != "silu":  # the kernels with the activation in their epilogue know SiLU only
-            gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
+        if s.activation != "silu" or s.token_gate_name is not None:
+            # (the kernels with the activation in their epilogue know SiLU only)
+            gu = ctx.scratch("gate_up", (n, self.wgu.shape[0]), ctx.dtype)
             linear(x, self.wgu, None, gu, ctx.scratch)
-            K.glu_act(gu, act, s.activation)
+            K.glu_act(gu, act, s.activation, s.act_limit, s.act_alpha, row_gate=s.token_gate_name is not None)
         elif not gated_linear(x, self.wgu, act):  # both projections and SiLU in one kernel, where one takes the sizes
             gu = ctx.scratch("gate_up", (n, 2 * s.intermediate), ctx.dtype)
             linear(x, self.wgu, None, gu, ctx.scratch)

@@ -69,6 +69,7 @@ class GroupedRMSNormSpec:
     eps: float
     weight_name: str  # checkpoint tensor of the gain, [dim]
     kind: str = "rmsnorm_grouped"
+    gain_offset: float = 0.0  # the gain is the stored tensor plus this (1.0: a weight stored around zero)
 
 
 @register_part("norm", "rmsnorm_grouped")
@@ -95,6 +96,11 @@ class GroupedRMSNorm(Norm):
     def scratch_elements_per_token(self) -> int:
         return self.spec.dim
 
+    def bind(self, params: dict[str, torch.Tensor]) -> None:
+        super().bind(params)
+        # the gain as the kernels read it: with an offset, the 32-bit sum (the stored tensor stays as loaded)
+        self.gain = self.weight if not self.spec.gain_offset else self.weight.float() + self.spec.gain_offset
+
     def forward(self, delta, residual: torch.Tensor, ctx: StepContext,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
         s: GroupedRMSNormSpec = self.spec
@@ -105,6 +111,8 @@ class GroupedRMSNorm(Norm):
             post = delta.norm
             if not isinstance(post, GroupedRMSNorm):
                 raise TypeError(f"{self.prefix}: a delta normed by {type(post).__name__} cannot be taken")
-            x, gain, groups, eps = delta.x, post.weight, post.spec.groups, post.spec.eps
-        K.add_norm_grouped(x, gain, groups, eps, residual, self.weight, s.groups, s.eps, out, rows=rows)
+            x, gain, groups, eps = delta.x, post.gain, post.spec.groups, post.spec.eps
+            if gain.dtype != self.gain.dtype:  # (the kernel reads both gains as one type)
+                gain = gain.to(self.gain.dtype)
+        K.add_norm_grouped(x, gain, groups, eps, residual, self.gain, s.groups, s.eps, out, rows=rows)
         return out

@@ -72,6 +72,39 @@ class RotaryInterleaved(RotaryNeox):
 
 
 @dataclass(frozen=True)
+class RotaryLinearSpec:
+    """Rotary angles with every frequency divided by `factor` (linear position scaling: position p turns
+    pair i by ``p * theta^(-2i / rotary_dim) / factor``); `factor` 1 is the plain table.  Either pairing."""
+
+    rotary_dim: int
+    theta: float
+    max_positions: int
+    factor: float = 1.0
+    pairing: str = "half"  # or "interleaved"
+    kind: str = "rotary_linear"
+
+
+@register_part("position", "rotary_linear")
+class RotaryLinear(RotaryNeox):
+    def __init__(self, spec: RotaryLinearSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.pairing not in K.ROTARY_PAIRINGS:
+            raise ValueError(f"pairing {spec.pairing!r}: one of {sorted(K.ROTARY_PAIRINGS)}")
+        if not spec.factor > 0 or not spec.theta > 0:
+            raise ValueError("linear scaling needs a positive factor and a positive base")
+        self.pairing = spec.pairing
+
+    def rotary(self, device: torch.device) -> tuple[torch.Tensor, int]:
+        s: RotaryLinearSpec = self.spec
+        if self._table is None or self._table.device != device:
+            # (frequencies in 64 bits, rounded once; the angle is the 32-bit product with the position)
+            i = torch.arange(s.rotary_dim // 2, dtype=torch.float64)
+            inv = (float(s.theta) ** (-2.0 * i / s.rotary_dim) / float(s.factor)).to(torch.float32)
+            self._table = K.rope_table(inv.to(device), s.max_positions)
+        return self._table, s.rotary_dim
+
+
+@dataclass(frozen=True)
 class RotaryYarnSpec:
     """Rotary angles whose slow pairs are stretched by `factor` (YaRN: Peng et al., "YaRN: Efficient
     Context Window Extension of Large Language Models").  With ``where(t) = rotary_dim * ln(original /

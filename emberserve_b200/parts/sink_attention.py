@@ -6,7 +6,13 @@
 * a chunk mask: the query at position p sees key j <= p only if ``j // chunk == p // chunk``,
   chunks counted from position 0 of the request, wherever a prompt was cut; and / or a window;
 * a sink: ``exp(sink[h])`` joins the softmax denominator of head h; it has no key and no value;
-* a gate per (token, head): head h's output is multiplied by ``sigmoid(x Wg^T)[h]``.
+* a gate per (token, head): head h's output is multiplied by ``sigmoid(x Wg^T)[h]``;
+* first keys that stay visible: with `keep_first`, keys at positions below it are seen by every later
+  query beside the window (or chunk), at their true positions; the cache holds their pages to the end;
+* value heads of a size of their own (`v_head_dim`), divided by their root mean square (`v_norm_eps`, no
+  gain) and turned by their position over their whole length (`value_position`, a rotary spec over
+  `v_head_dim` numbers) before they are cached; each head's sum over the values is then turned back by
+  the query's position, so that the output depends on distances only.
 
 ``[q | k | (v) | gate] = x W^T + b`` is one product; one kernel rotates, norms and writes the
 cache; the attention kernel applies mask, sink and gate; then ``o = attn Wo^T``.  Scores, softmax,
@@ -50,6 +56,10 @@ class SinkAttentionSpec:
     chunk: int | None = None
     window: int | None = None
     kind: str = "sink_attention"
+    keep_first: int = 0  # keys below this position stay visible beside the window / chunk
+    v_head_dim: int | None = None  # numbers per value head (None: head_dim)
+    v_norm_eps: float | None = None  # unit RMS of every value head
+    value_position: Any = None  # rotary spec over v_head_dim numbers: values turned when cached, the sum turned back
 
 
 @register_part("mixer", "sink_attention")
@@ -65,32 +75,44 @@ class SinkAttention(Mixer):
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if spec.head_dim % 8 or spec.head_dim > 256:
             raise ValueError(f"head_dim={spec.head_dim}: the attention kernels take multiples of 8 up to 256")
+        self.v_dim = spec.head_dim if spec.v_head_dim is None else spec.v_head_dim
+        if self.v_dim % 8 or self.v_dim > 256:
+            raise ValueError(f"v_head_dim={self.v_dim}: the attention kernels take multiples of 8 up to 256")
+        if spec.v_name is None and (self.v_dim != spec.head_dim or spec.v_norm_eps is not None
+                                    or spec.value_position is not None):
+            raise ValueError("values that are the keys as projected have the keys' size, no norm and no rotation")
         self.q_size = spec.num_heads * spec.head_dim
         self.kv_size = spec.num_kv_heads * spec.head_dim
-        self.v_cols = 0 if spec.v_name is None else self.kv_size
+        self.o_size = spec.num_heads * self.v_dim
+        self.v_cols = 0 if spec.v_name is None else spec.num_kv_heads * self.v_dim
         self.gate_at = self.q_size + self.kv_size + self.v_cols
         # the gate's columns are padded so that a row of the product stays 16-byte aligned
         self.gate_cols = 0 if spec.gate_name is None else -(-spec.num_heads // 8) * 8
         self.cols = self.gate_at + self.gate_cols
         self.position = self.shared.get("position", spec.position) if spec.position is not None else None
+        self.value_position = (self.shared.get("position", spec.value_position)
+                               if spec.value_position is not None else None)
+        if self.value_position is not None and self.value_position.spec.rotary_dim != self.v_dim:
+            raise ValueError("the rotation of the values covers the whole value head")
         self._sink32: torch.Tensor | None = None
 
     def cache_need(self) -> PagedKV:
         s: SinkAttentionSpec = self.spec
-        return PagedKV(s.num_kv_heads, s.head_dim, s.window, s.chunk)
+        return PagedKV(s.num_kv_heads, s.head_dim, s.window, s.chunk, keep_first=int(s.keep_first or 0),
+                       v_head_dim=None if self.v_dim == s.head_dim else self.v_dim)
 
     def param_specs(self) -> dict[str, ParamSpec]:
         s: SinkAttentionSpec = self.spec
         q, kv = self.q_size, self.kv_size
         rows = [(s.q_name, s.q_bias_name, (0, q)), (s.k_name, s.k_bias_name, (q, q + kv))]
         if s.v_name is not None:
-            rows.append((s.v_name, s.v_bias_name, (q + kv, q + 2 * kv)))
+            rows.append((s.v_name, s.v_bias_name, (q + kv, q + kv + self.v_cols)))
         if s.gate_name is not None:
             rows.append((s.gate_name, None, (self.gate_at, self.gate_at + s.num_heads)))
         # (rows that no tensor fills, the gate's padding and absent biases, stay zero)
         specs = {
             "wqkv": ParamSpec((self.cols, s.hidden), [Source(n, r) for n, _, r in rows]),
-            "wo": ParamSpec((s.hidden, q), [Source(s.o_name)]),
+            "wo": ParamSpec((s.hidden, self.o_size), [Source(s.o_name)]),
         }
         biased = [(b, r) for _, b, r in rows if b is not None]
         if biased:
@@ -107,7 +129,7 @@ class SinkAttention(Mixer):
         return ["wqkv", "wo"]
 
     def scratch_elements_per_token(self) -> int:
-        return self.cols + self.q_size + self.spec.hidden
+        return self.cols + self.o_size + self.spec.hidden
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVHandle) -> torch.Tensor:
         s: SinkAttentionSpec = self.spec
@@ -119,27 +141,36 @@ class SinkAttention(Mixer):
             r = self.position.rotary(ctx.device)
             if r is not None:
                 (table, rot), pairing = r, self.position.pairing
+        vtable, vpairing = None, "half"
+        if self.value_position is not None:
+            vtable, vpairing = self.value_position.rotary(ctx.device)[0], self.value_position.pairing
         K.qk_prep(proj, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions, ctx.row_of_token, table, rot,
-                  pairing, s.qk_norm_eps, cache.k, cache.v, cache.block_tables, s.v_name is None, cache.write)
-        out = ctx.scratch("attn_out", (n, self.q_size), ctx.dtype)
+                  pairing, s.qk_norm_eps, cache.k, cache.v, cache.block_tables, s.v_name is None, cache.write,
+                  v_norm_eps=s.v_norm_eps, v_table=vtable, v_pairing=vpairing)
+        out = ctx.scratch("attn_out", (n, self.o_size), ctx.dtype)
+        extras = dict(keep_first=int(s.keep_first or 0), out_table=vtable, out_pairing=vpairing,
+                      positions=ctx.positions if vtable is not None else None)
         gate = proj[:, self.gate_at:self.gate_at + self.gate_cols] if self.gate_cols else None
         kern = ctx.extra.get("attn_kernel", "auto")
         if ctx.all_decode and n == b:
             # one token per row: the keys of a row are split over blocks when rows are few.  A chunk
             # or a window bounds the keys a query reads, whatever the context.
             reach = min(x for x in (ctx.max_ctx_len, s.chunk, s.window) if x)
+            if s.keep_first and reach < ctx.max_ctx_len:
+                reach = min(ctx.max_ctx_len, reach + int(s.keep_first))
             splits = decode_splits(b, s.num_kv_heads, reach, K.sm_count(ctx.device))
             scratch = None
             if splits > 1:
-                nbytes = K.attention_scratch_bytes(b, s.num_heads, s.head_dim, splits)
+                nbytes = K.attention_scratch_bytes(b, s.num_heads, self.v_dim, splits)
                 scratch = ctx.scratch("attn_partials", (nbytes // 4,), torch.float32)
             K.paged_attention_masked(proj, out, cache.k, cache.v, cache.block_tables, ctx.cu_q, ctx.starts, b, n,
                                      s.num_heads, s.num_kv_heads, s.head_dim, s.scale, 1, window=s.window,
                                      chunk=s.chunk, sinks=self._sink32, gate=gate, splits=splits, scratch=scratch,
-                                     kernel=kern)
+                                     kernel=kern, **extras)
         else:
             K.paged_attention_masked(proj, out, cache.k, cache.v, cache.block_tables, ctx.cu_q, ctx.starts, b, n,
                                      s.num_heads, s.num_kv_heads, s.head_dim, s.scale, ctx.max_q_len,
-                                     window=s.window, chunk=s.chunk, sinks=self._sink32, gate=gate, kernel=kern)
+                                     window=s.window, chunk=s.chunk, sinks=self._sink32, gate=gate, kernel=kern,
+                                     **extras)
         y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
         return linear(out, self.wo, None, y, ctx.scratch)

@@ -15,12 +15,12 @@ import numpy as np
 import torch
 
 
-def embedding(table, tokens, residual, deferred=None):
+def embedding(table, tokens, residual, deferred=None, scale=1.0):
     n = residual.shape[0]
     tok = tokens[:n].long()
     if deferred is not None and bool((tok < 0).any()):
         tok = torch.where(tok < 0, deferred.long()[(-(tok + 1)).clamp(min=0)], tok)
-    residual.copy_(table[tok].float())
+    residual.copy_(table[tok].float() * torch.tensor(scale, dtype=torch.float32))
 
 
 def add_rmsnorm(delta, residual, weight, out, eps, rows=None, num_rows=None):
@@ -254,10 +254,51 @@ def _glu_activation(g, act):
     return g / (1 + torch.exp(-g))
 
 
-def glu_act(gate_up, out, act):
+def _glu(g, u, act, limit, alpha):
+    if act == "swiglu_capped":
+        g = g.clamp(max=limit)
+        u = u.clamp(-limit, limit)
+        return g * torch.sigmoid(alpha * g) * (u + 1)
+    return _glu_activation(g, act) * u
+
+
+def glu_act(gate_up, out, act, limit=0.0, alpha=1.0, row_gate=False):
     i = out.shape[1]
-    g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
-    out.copy_((_glu_activation(g, act) * u).to(out.dtype))
+    g, u = gate_up[:, :i].float(), gate_up[:, i:2 * i].float()
+    y = _glu(g, u, act, limit, alpha)
+    if row_gate:
+        y = y * torch.sigmoid(gate_up[:, 2 * i].float())[:, None]
+    out.copy_(y.to(out.dtype))
+
+
+def add_cast(delta, residual, out):
+    if delta is not None:
+        residual += delta[:residual.shape[0]].float()
+    out.copy_(residual.to(out.dtype))
+
+
+def token_gate(z, table, col0, tokens, out, deferred=None):
+    n, c = z.shape
+    tok = tokens[:n].long()
+    if deferred is not None and bool((tok < 0).any()):
+        tok = torch.where(tok < 0, deferred.long()[(-(tok + 1)).clamp(min=0)], tok)
+    v = z.float()
+    g = 0.5 * v * (1 + torch.tanh(math.sqrt(2 / math.pi) * (v + 0.044715 * v ** 3)))
+    out.copy_((g * table[tok, col0:col0 + c].float()).to(out.dtype))
+
+
+def depth_mix(delta, gain, eps, residual, hist, weights, count):
+    n = residual.shape[0]
+    x = residual
+    if delta is not None:
+        d = delta[:n].float()
+        if gain is not None:
+            d = d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * gain.float()
+        x = residual + d
+    hist[count - 1].copy_(x)
+    if weights is not None:
+        x = sum(weights[j] * hist[j] for j in range(count))
+    residual.copy_(x)
 
 
 def causal_taps(x, weight, state, slots, cu_q, row_of_token, out, num_rows, bias=None, identity=True):
@@ -362,10 +403,11 @@ def moe_max_tiles(num_pairs, num_experts, tile_rows):
     return num_pairs // tile_rows + min(num_experts, num_pairs)
 
 
-def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_tiles, align=1, big=None, inv=None):
+def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_tiles, align=1, big=None, inv=None,
+              scoring="softmax"):
     assert align == 1, "the aligned layout belongs to the GPU path"
     n, e = logits.shape
-    s = torch.softmax(logits.float(), -1)
+    s = torch.sigmoid(logits.float()) if scoring == "sigmoid" else torch.softmax(logits.float(), -1)
     chosen = torch.zeros(n, top, dtype=torch.long)
     z = logits.clone()
     for k in range(top):
@@ -384,7 +426,8 @@ def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_t
     offsets[1:e + 1] = torch.cumsum(counts, 0).to(torch.int32)
 
 
-def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out, kernel="auto"):
+def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out, kernel="auto", in_scale=None, limit=0.0,
+           alpha=1.0):
     e, ff2, k = wgu.shape
     ff = ff2 // 2
     off = offsets.tolist()
@@ -393,8 +436,12 @@ def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out, kernel="auto")
         if hi <= lo:
             continue
         rows = x[(perm[lo:hi] // top).long()].float()
-        y = (rows @ wgu[ex].float().t()).to(out.dtype).float()
-        out[lo:hi] = (_glu_activation(y[:, :ff], act) * y[:, ff:]).to(out.dtype)
+        y = rows @ wgu[ex].float().t()
+        if in_scale is not None:
+            y = y * in_scale[perm[lo:hi].long()][:, None]
+        if act != "swiglu_capped":  # (that one works on the unrounded sums)
+            y = y.to(out.dtype).float()
+        out[lo:hi] = _glu(y[:, :ff], y[:, ff:], act, limit, alpha).to(out.dtype)
 
 
 def moe_down(act, wdown, perm, offsets, plan, max_tiles, y, kernel="auto"):
@@ -407,9 +454,15 @@ def moe_down(act, wdown, perm, offsets, plan, max_tiles, y, kernel="auto"):
         y[perm[lo:hi].long()] = (act[lo:hi].float() @ wdown[ex].float().t()).to(act.dtype).float()
 
 
-def moe_combine(y, weights, out, top):
+def moe_combine(y, weights, out, top, extra=None):
     n, h = out.shape
-    out.copy_((y[:n * top].view(n, top, h) * weights.view(-1)[:n * top].view(n, top, 1)).sum(1).to(out.dtype))
+    rows = y[:n * top].view(n, top, h)
+    if weights is not None:
+        rows = rows * weights.view(-1)[:n * top].view(n, top, 1)
+    total = rows.sum(1)
+    if extra is not None:
+        total = total + extra.float()
+    out.copy_(total.to(out.dtype))
 
 
 def unary_act(x, out, act):
@@ -426,21 +479,29 @@ def unary_act(x, out, act):
 
 
 def qk_prep(proj, num_heads, num_kv_heads, head_dim, positions, row_of_token, table, rot_dims, pairing, norm_eps,
-            kcache, vcache, block_tables, values_are_keys, write=True):
-    n, d = proj.shape[0], head_dim
+            kcache, vcache, block_tables, values_are_keys, write=True, v_norm_eps=None, v_table=None,
+            v_pairing="half"):
+    n, d, dv = proj.shape[0], head_dim, vcache.shape[3]
     nq, nk = num_heads * d, num_kv_heads * d
     pos = positions[:n].long()
     q = proj[:, :nq].float().view(n, num_heads, d)
     k_raw = proj[:, nq:nq + nk]
     k = k_raw.float().view(n, num_kv_heads, d)
-    v = k_raw if values_are_keys else proj[:, nq + nk:nq + 2 * nk]
+    v = k_raw if values_are_keys else proj[:, nq + nk:nq + nk + num_kv_heads * dv]
     if table is not None and rot_dims:
         cs = table[pos][:, None]
         q, k = _rotate_pairs(q, cs, rot_dims, pairing), _rotate_pairs(k, cs, rot_dims, pairing)
     if norm_eps is not None:
         q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + norm_eps)
         k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + norm_eps)
-    vv = v.reshape(n, num_kv_heads, d).clone()
+    vv = v.reshape(n, num_kv_heads, dv).clone()
+    if v_norm_eps is not None or v_table is not None:
+        vf = vv.float()
+        if v_norm_eps is not None:
+            vf = vf * torch.rsqrt(vf.pow(2).mean(-1, keepdim=True) + v_norm_eps)
+        if v_table is not None:
+            vf = _rotate_pairs(vf, v_table[pos][:, None], dv, v_pairing)
+        vv = vf
     proj[:, :nq] = q.reshape(n, nq).to(proj.dtype)
     if not write:
         return
@@ -452,8 +513,10 @@ def qk_prep(proj, num_heads, num_kv_heads, head_dim, positions, row_of_token, ta
 
 def paged_attention_masked(q, out, kcache, vcache, block_tables, cu_q, starts, num_rows, num_tokens, num_heads,
                            num_kv_heads, head_dim, scale, max_q_len, window=None, chunk=None, sinks=None, gate=None,
-                           splits=1, scratch=None, kernel="auto"):
+                           splits=1, scratch=None, kernel="auto", keep_first=0, out_table=None, out_pairing="half",
+                           positions=None):
     page_size = kcache.shape[2]
+    dv = vcache.shape[3]
     groups = num_heads // num_kv_heads
     cu, st = cu_q.tolist(), starts.tolist()
     for b in range(num_rows):
@@ -466,28 +529,36 @@ def paged_attention_masked(q, out, kcache, vcache, block_tables, cu_q, starts, n
             lo = max(lo, st[b] - window + 1)
         if chunk:
             lo = max(lo, (st[b] // chunk) * chunk)
-        keys = torch.arange(lo, ctx)
+        kept = min(keep_first or 0, lo) if (window or chunk) else 0
+        keys = torch.cat((torch.arange(0, kept), torch.arange(lo, ctx)))
         pages = block_tables[b, keys // page_size].long()
         k = kcache[pages, :, keys % page_size, :].float().repeat_interleave(groups, dim=1).permute(1, 0, 2)
         v = vcache[pages, :, keys % page_size, :].float().repeat_interleave(groups, dim=1).permute(1, 0, 2)
         qq = q[q0:q1, : num_heads * head_dim].float().view(qlen, num_heads, head_dim).permute(1, 0, 2)
         scores = torch.matmul(qq, k.transpose(-1, -2)) * scale  # [H, qlen, T]
         qpos = torch.arange(st[b], ctx)[:, None]
-        hidden = keys[None, :] > qpos
+        hidden = torch.zeros(qlen, keys.numel(), dtype=torch.bool)
         if window:
             hidden = hidden | (keys[None, :] <= qpos - window)
         if chunk:
             hidden = hidden | (keys[None, :] // chunk != qpos // chunk)
+        if keep_first:
+            hidden = hidden & (keys[None, :] >= keep_first)
+        hidden = hidden | (keys[None, :] > qpos)
         scores = scores.masked_fill(hidden, float("-inf"))
         mx = scores.max(-1, keepdim=True).values
         e = torch.exp(scores - mx)
         den = e.sum(-1, keepdim=True)
         if sinks is not None:
             den = den + torch.exp(sinks.float()[:, None, None] - mx)
-        o = torch.matmul(e / den, v).permute(1, 0, 2)  # [qlen, H, D]
+        o = torch.matmul(e / den, v).permute(1, 0, 2)  # [qlen, H, DV]
+        if out_table is not None:
+            cs = out_table[positions[q0:q1].long()][:, None].clone()
+            cs[..., 1] = -cs[..., 1]  # back by the same angle
+            o = _rotate_pairs(o, cs, dv, out_pairing)
         if gate is not None:
             o = o * torch.sigmoid(gate[q0:q1, :num_heads].float())[:, :, None]
-        out[q0:q1] = o.reshape(qlen, num_heads * head_dim).to(out.dtype)
+        out[q0:q1] = o.reshape(qlen, num_heads * dv).to(out.dtype)
 
 
 def norm_mean2(a, b, gain_a, gain_b, eps, out):
@@ -580,7 +651,8 @@ ALL = ["gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rms
        "stream_inject", "add_norm_grouped", "glu_act", "causal_taps", "latent_prep", "rope_inplace",
        "latent_attention_scratch_bytes", "latent_attention", "heads_gate", "moe_tile_rows", "moe_max_tiles",
        "moe_route", "moe_up", "moe_down", "moe_combine", "unary_act", "qk_prep", "paged_attention_masked",
-       "norm_mean2", "matrix_recurrence", "mlstm_gates", "group_norm_gate", "rglru_scan"]
+       "norm_mean2", "matrix_recurrence", "mlstm_gates", "group_norm_gate", "rglru_scan", "add_cast", "token_gate",
+       "depth_mix"]
 
 
 def install(monkeypatch) -> None:
