@@ -985,8 +985,57 @@ def run_dedizen(args) -> dict:
                                    {k: (list(v) if isinstance(v, tuple) else v) for k, v in z.items()}, runs)
 
 
-def run_design_beside_qwen2(args, key: str, label: str, size: str, dam, qwen, z: dict, runs: int) -> dict:
-    """Prompt and decode steps of one design and of the dense Qwen2 shape beside it, with device time per kernel."""
+# ---------------------------------------------------------------------------------------
+# --workload vonulix: the design with windowed attention that keeps its first keys and turns its values,
+# sigmoid-scored experts beside a shared expert, a token input per layer and the depth average; beside
+# Damolorn with the same routed experts and the dense Qwen2 shape with the same heads and window.
+
+VONULIX_SIZES = {
+    # width; heads / key heads / head size; window / kept first keys; experts / top / expert ff; shared ff;
+    # columns of the second embedding table per layer
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=64, experts=64, top=6, ff=1408,
+               shared_ff=1408, side=256),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, window=1024, keep=64, experts=32, top=4, ff=3072,
+               shared_ff=3072, side=256),
+}
+
+
+def vonulix_config(size: str, vocab: int = 32000, layers: int = 6) -> dict:
+    z = VONULIX_SIZES[size]
+    layer = {"type": "attention",
+             "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                       "mask": {"size": z["window"], "keep_first": z["keep"]}, "scale": z["dim"] ** -0.5,
+                       "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0}}},
+             "mlp": {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]},
+                     "expert": {"ff": z["ff"], "limit": 7.0}, "shared": {"ff": z["shared_ff"], "limit": 7.0}}}
+    return {"architecture": "Vonulix", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": z["width"] ** 0.5}, "token_side": {"dim": z["side"]},
+            "layers": [layer] * layers, "max_positions": 8192}
+
+
+def run_vonulix(args) -> dict:
+    from emberserve_b200.config.damolorn import DamolornConfig
+    from emberserve_b200.config.model import Qwen2Config
+    from emberserve_b200.config.vonulix import VonulixConfig
+
+    z = VONULIX_SIZES[args.vonulix_size]
+    von = VonulixConfig.from_dict(vonulix_config(args.vonulix_size))
+    runs = len(von.layers)
+    qwen = Qwen2Config.from_dict(dict(
+        SHAPE_7B, vocab_size=32000, hidden_size=z["width"], num_attention_heads=z["heads"],
+        num_key_value_heads=z["kv_heads"], head_dim=128, intermediate_size=(z["top"] * z["ff"] + z["shared_ff"]),
+        num_hidden_layers=runs, max_position_embeddings=8192, sliding_window=z["window"], use_sliding_window=True,
+        max_window_layers=0, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    others = []
+    if args.vonulix_size in DAMOLORN_SIZES and DAMOLORN_SIZES[args.vonulix_size]["ff"] == z["ff"]:
+        others.append(("damolorn", "Damolorn", DamolornConfig.from_dict(damolorn_config(args.vonulix_size))))
+    return run_design_beside_qwen2(args, "vonulix", "Vonulix", args.vonulix_size, von, qwen, z, runs, others)
+
+
+def run_design_beside_qwen2(args, key: str, label: str, size: str, dam, qwen, z: dict, runs: int,
+                            others: list | None = None) -> dict:
+    """Prompt and decode steps of one design and of the dense Qwen2 shape beside it (and of `others`:
+    (key, label, config) of further models), with device time per kernel."""
     import torch
 
     from emberserve_b200 import kernels as K
@@ -1095,9 +1144,12 @@ def run_design_beside_qwen2(args, key: str, label: str, size: str, dam, qwen, z:
         return {"workload": key, "size": size, "only": args.only, key: measure(dam, label)}
     ours = measure(dam, label)
     beside = measure(qwen, "Qwen2 dense")
-    return {"workload": key, "size": size, "dtype": args.dtype, "layer_runs": runs,
-            "context": ctx_len, "shape": z, "peaks": peaks, key: ours, "qwen2": beside,
-            "data": "synthetic: uniform random token ids, random weights N(0,0.02) seed 0"}
+    out = {"workload": key, "size": size, "dtype": args.dtype, "layer_runs": runs,
+           "context": ctx_len, "shape": z, "peaks": peaks, key: ours, "qwen2": beside,
+           "data": "synthetic: uniform random token ids, random weights N(0,0.02) seed 0"}
+    for okey, olabel, ocfg in others or ():
+        out[okey] = measure(ocfg, olabel)
+    return out
 
 
 def main() -> int:
@@ -1107,16 +1159,19 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b", "damolorn", "dedizen"],
+    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b", "damolorn", "dedizen", "vonulix"],
                     default="decode-7b",
                     help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests; "
                          "mixed-32b: chunked prefill of long prompts beside decode at the 32B shape; fp32-7b: "
                          "the true 32-bit path (the headline line runs the last three as child processes); "
                          "damolorn: prompt and decode steps of the Damolorn design at --damolorn-size beside the "
                          "dense Qwen2 shape of equal width, layer runs and active feed-forward width; dedizen: the "
-                         "same for the Dedizen design at --dedizen-size (equal width, layers and feed-forward weights)")
+                         "same for the Dedizen design at --dedizen-size (equal width, layers and feed-forward weights); "
+                         "vonulix: the same for the Vonulix design at --vonulix-size, beside Qwen2 with the same "
+                         "heads, window and active feed-forward width and beside Damolorn with the same experts")
     ap.add_argument("--damolorn-size", choices=sorted(DAMOLORN_SIZES), default="2k")
     ap.add_argument("--dedizen-size", choices=sorted(DEDIZEN_SIZES), default="2k")
+    ap.add_argument("--vonulix-size", choices=sorted(VONULIX_SIZES), default="2k")
     ap.add_argument("--no-extras", action="store_true",
                     help="the headline line without the points that need other models or kernels alone")
     ap.add_argument("--requests", type=int, default=256)
@@ -1175,6 +1230,9 @@ def main() -> int:
         return 0
     if args.workload == "dedizen":
         print(json.dumps(run_dedizen(args)))
+        return 0
+    if args.workload == "vonulix":
+        print(json.dumps(run_vonulix(args)))
         return 0
     if args.only == "kernel":
         print(json.dumps(run_kernel(args)))

@@ -89,12 +89,20 @@ decode_attention_mma_kernel(const DecodeParams p) {
 
     // this block's tiles (16 keys each, aligned to absolute positions), and this warp's
     const int tile_lo = k_begin / DEC_TK, tile_hi = (ctx - 1) / DEC_TK;  // inclusive
-    const int ntiles = tile_hi - tile_lo + 1;
+    // first keys that stay visible although the window has passed them: the tiles that hold them (and
+    // lie wholly before tile_lo) come first in the list that splits and warps share out
+    const int keep = min(p.keep, k_begin);
+    const int nhead = min((keep + DEC_TK - 1) / DEC_TK, tile_lo);
+    const int ntiles = nhead + tile_hi - tile_lo + 1;
     const int per_split = (ntiles + p.splits - 1) / p.splits;
-    const int t_begin = tile_lo + split * per_split;
-    const int t_end = min(tile_hi + 1, t_begin + per_split);
+    const int t_begin = split * per_split;     // places in the list; tile_at gives the tile
+    const int t_end = min(ntiles, t_begin + per_split);
     const int my_first = t_begin + warp;
     const int my_count = my_first < t_end ? (t_end - my_first + DEC_WARPS - 1) / DEC_WARPS : 0;
+    auto tile_at = [&](int i) {  // the warp's i-th tile
+        const int t = my_first + i * DEC_WARPS;
+        return t < nhead ? t : tile_lo + (t - nhead);
+    };
 
     unsigned char* ring = smem_raw + warp * WARP_BYTES;
     const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
@@ -104,7 +112,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
     const int new_key = (p.fused && p.write_kv) ? ctx - 1 : -1;
 
     auto issue_tile = [&](int i) {  // stream the warp's i-th tile into stage i % DEC_STAGES
-        const int tile = my_first + i * DEC_WARPS;
+        const int tile = tile_at(i);
         const uint32_t kdst = ring_addr + (i % DEC_STAGES) * 2 * TILE_BYTES;
         const uint32_t vdst = kdst + TILE_BYTES;
         constexpr int ROWS_PER_IT = 32 / CH;
@@ -118,7 +126,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
             for (int it = 0; it < DEC_TK / ROWS_PER_IT; ++it) {
                 const int row = it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
                 const int key = key0 + row;
-                const bool valid = key >= k_begin && key < ctx && key != new_key;
+                const bool valid = (key >= k_begin || key < keep) && key < ctx && key != new_key;
                 const uint32_t sw = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
                 cp_async16(kdst + sw, valid ? ksrc + it * 256 : p.kc, valid);
                 cp_async16(vdst + sw, valid ? vsrc + it * 256 : p.vc, valid);
@@ -129,7 +137,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
         for (int it = 0; it < DEC_TK / ROWS_PER_IT; ++it) {
             const int row = it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
             const int key = tile * DEC_TK + row;
-            const bool valid = key >= k_begin && key < ctx && key != new_key;
+            const bool valid = (key >= k_begin || key < keep) && key < ctx && key != new_key;
             size_t off = 0;
             if (valid) {
                 const int page = table[key / p.page_size];
@@ -146,7 +154,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
     int issued = 0;
 #pragma unroll
     for (int s = 0; s < DEC_STAGES; ++s) {
-        if (s < my_count && my_first + s * DEC_WARPS == tile_hi) break;
+        if (s < my_count && tile_at(s) == tile_hi) break;
         if (s < my_count) issue_tile(s);
         cp_async_commit();
         ++issued;
@@ -208,8 +216,8 @@ decode_attention_mma_kernel(const DecodeParams p) {
         __syncwarp();
         const uint32_t kst = ring_addr + (i % DEC_STAGES) * 2 * TILE_BYTES;
         const uint32_t vst = kst + TILE_BYTES;
-        const int key0 = (my_first + i * DEC_WARPS) * DEC_TK;
-        if (new_key >= 0 && my_first + i * DEC_WARPS == tile_hi) {
+        const int key0 = tile_at(i) * DEC_TK;
+        if (new_key >= 0 && tile_at(i) == tile_hi) {
             // the row's own key and value: from the qkv row into the cache and into this tile
             const int row = new_key - key0;
             const bf16* kraw = p.q + (size_t)tok * p.q_stride + (size_t)(p.nh + hk) * D;
@@ -270,7 +278,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int key = key0 + n * 8 + (lane & 3) * 2 + e;
-                    if (key < k_begin || key >= ctx) { s[n][e] = -INFINITY; s[n][2 + e] = -INFINITY; }
+                    if ((key < k_begin && key >= keep) || key >= ctx) { s[n][e] = -INFINITY; s[n][2 + e] = -INFINITY; }
                 }
         }
         float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -354,21 +362,50 @@ decode_attention_mma_kernel(const DecodeParams p) {
     }
     __syncthreads();
 
-    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
-        const int g = idx / D, d = idx % D;
-        float M = -INFINITY;
+    // `count` columns of head g of the group, merged over the warps: acc[j] for column cols[j], M and L
+    auto merged = [&](int g, const int* cols, int count, float* acc, float& M, float& L) {
+        M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w)
             M = fmaxf(M, reinterpret_cast<const float*>(smem_raw + w * WARP_BYTES)[g]);
-        float acc = 0.f, L = 0.f;
+        L = 0.f;
+        for (int j = 0; j < count; ++j) acc[j] = 0.f;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
             const float* base = reinterpret_cast<const float*>(smem_raw + w * WARP_BYTES);
             const float mw = base[g];
             const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
             L += base[16 + g] * f;
-            acc += base[32 + g * D + d] * f;
+            for (int j = 0; j < count; ++j) acc[j] += base[32 + g * D + cols[j]] * f;
         }
+    };
+    auto scale_of = [&](int g, float M, float L) {  // 1 / denominator, with the head's sink and gate
+        if (p.sinks) L += exp2f(p.sinks[hk * G + g] * 1.4426950408889634f - M);
+        float y = 1.f / L;
+        if (p.gate) y *= 1.f / (1.f + expf(-__bfloat162float(p.gate[(size_t)tok * p.gate_stride + hk * G + g])));
+        return y;
+    };
+    if (p.splits == 1 && p.out_table) {
+        // the values were turned by their positions before they were cached: a thread takes both numbers
+        // of a pair and turns them back by the query's position
+        const float* cs = p.out_table + (size_t)(ctx - 1) * (D / 2) * 2;
+        for (int idx = threadIdx.x; idx < G * (D / 2); idx += DEC_WARPS * 32) {
+            const int g = idx / (D / 2), i = idx % (D / 2);
+            const int cols[2] = {p.out_pairing ? 2 * i : i, p.out_pairing ? 2 * i + 1 : i + D / 2};
+            float acc[2], M, L;
+            merged(g, cols, 2, acc, M, L);
+            const float y = scale_of(g, M, L), u = acc[0] * y, w = acc[1] * y;
+            const float cc = cs[2 * i], sn = cs[2 * i + 1];
+            const size_t prow = (size_t)tok * p.nh + (size_t)hk * G + g;
+            p.out[prow * D + cols[0]] = __float2bfloat16_rn(u * cc + w * sn);
+            p.out[prow * D + cols[1]] = __float2bfloat16_rn(w * cc - u * sn);
+        }
+        return;
+    }
+    for (int idx = threadIdx.x; idx < G * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, d = idx % D;
+        float acc, M, L;
+        merged(g, &d, 1, &acc, M, L);
         const size_t prow = (size_t)tok * p.nh + (size_t)hk * G + g;
         if (p.splits == 1) {
             if (p.sinks) L += exp2f(p.sinks[hk * G + g] * 1.4426950408889634f - M);

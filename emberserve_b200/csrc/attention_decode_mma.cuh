@@ -37,9 +37,11 @@ struct DecodeParams {
     const int* positions = nullptr; // [N] position of each token of the step
 };
 
-// Whether the tensor-core kernels for masked attention take these options (all of them take chunk, sinks
-// and gate; kept first keys and a result that is turned back are taken by the generic kernel alone).
-inline bool masked_mma_takes(const DecodeParams& p) { return p.keep == 0 && p.out_table == nullptr; }
+// The key tiles that a block walks when the first `keep` keys stay visible beside the window: `nhead`
+// tiles from position 0 (those that lie wholly before the window's first tile), then the tiles from kt0.
+__host__ __device__ __forceinline__ int tile_start(int t, int nhead, int kt0, int bk) {
+    return t < nhead ? t * bk : kt0 + (t - nhead) * bk;
+}
 
 // The first key that the query at position p may see.
 __host__ __device__ __forceinline__ int first_visible(int p, int window, int chunk) {
@@ -59,7 +61,8 @@ bool decode_fused_supported(int D, int G, int rot, long long q_stride, const voi
 bool prefill_mma_supported(int dtype, int D, long long q_stride, const void* q, const void* out,
                            const void* kc, const void* vc);
 int run_prefill_mma(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream);
-// The same kernel with a chunk mask, sinks and a gate per head (DecodeParams::chunk, sinks, gate); the
+// The same kernel with a chunk mask, sinks, a gate per head, kept first keys and a result that is turned
+// back (DecodeParams::chunk, sinks, gate, keep, out_table); the
 // softmax weights enter the second product as two bfloat16 terms (value and remainder), so that they
 // carry 16 bits of mantissa instead of 8.
 int run_prefill_mma_masked(const DecodeParams& p, int B, int D, int max_q_len, cudaStream_t stream);

@@ -52,12 +52,6 @@ struct AttnParams {
     const int* positions = nullptr; // [N] position of every token of the step (for the merge of key splits)
 };
 
-// The key tiles that a block walks when the first `keep` keys stay visible beside the window: `nhead`
-// tiles from position 0 (those that lie wholly before the window's first tile), then the tiles from kt0.
-__device__ __forceinline__ int tile_start(int t, int nhead, int kt0, int bk) {
-    return t < nhead ? t * bk : kt0 + (t - nhead) * bk;
-}
-
 template <typename T, int VEC> struct VecLoad;
 template <> struct VecLoad<float, 4> {
     static __device__ __forceinline__ void load(const float* p, float* dst) {
@@ -434,7 +428,7 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
     d.keep = keep; d.out_table = out_table; d.out_pairing = out_pairing; d.positions = positions;
     if (!plain) {
         // prompt portions on the tensor cores where the sizes allow; everything else on the generic kernel
-        const bool mma_form = DV == D && masked_mma_takes(d);
+        const bool mma_form = DV == D;
         if (!mma_form) {
             if (dtype == EMS_F32) return run_attention<float>(p, B, N, max_q_len, stream);
             if (dtype == EMS_BF16) return run_attention<bf16>(p, B, N, max_q_len, stream);

@@ -97,7 +97,12 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     const int k_begin = first_visible(p_lo, p.window, chunk);
     const int k_end = p_hi + 1;
     const int kt0 = (k_begin / PF_BK) * PF_BK;
-    const int ntiles = (k_end - kt0 + PF_BK - 1) / PF_BK;
+    // first keys that stay visible although the window of the block's first query has passed them: the
+    // tiles that hold them (and lie wholly before kt0) are walked first
+    const int keep_raw = EXT ? p.keep : 0;
+    const int keep = min(keep_raw, k_begin);
+    const int nhead = min((keep + PF_BK - 1) / PF_BK, kt0 / PF_BK);
+    const int ntiles = nhead + (k_end - kt0 + PF_BK - 1) / PF_BK;
     const int* table = p.bt + (size_t)b * p.bt_stride;
 
     // queries of the block -> shared memory (rows past the request are zeros)
@@ -111,13 +116,13 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     }
     auto issue_tile = [&](int t) {
         const uint32_t kdst = kv_s + (t & 1) * 2 * KV_BYTES, vdst = kdst + KV_BYTES;
-        const int kt = kt0 + t * PF_BK;
+        const int kt = tile_start(t, nhead, kt0, PF_BK);
         if (PAGE16) {
             // warp w fetches keys [kt + 16 w', kt + 16 w' + 16) for w' = w, w + 4, ... : one page each
             constexpr int ROWS_PER_IT = 32 / CH;
             for (int grp = warp; grp < PF_BK / 16; grp += PF_WARPS) {
                 const int key0 = kt + grp * 16;
-                const bool any = key0 < k_end && key0 + 16 > k_begin;
+                const bool any = key0 < k_end && (key0 + 16 > k_begin || key0 < keep);
                 size_t base = 0;
                 if (any) {
                     const int page = table[key0 / p.page_size];
@@ -129,7 +134,7 @@ prefill_attention_mma_kernel(const DecodeParams p) {
                 for (int it = 0; it < 16 / ROWS_PER_IT; ++it) {
                     const int row = grp * 16 + it * ROWS_PER_IT + lane / CH, chunk = lane % CH;
                     const int key = kt + row;
-                    const bool valid = key >= k_begin && key < k_end;
+                    const bool valid = (key >= k_begin || key < keep) && key < k_end;
                     const uint32_t sw = row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
                     pf_cp_async16(kdst + sw, valid ? ksrc + it * 256 : p.kc, valid);
                     pf_cp_async16(vdst + sw, valid ? vsrc + it * 256 : p.vc, valid);
@@ -140,7 +145,7 @@ prefill_attention_mma_kernel(const DecodeParams p) {
         for (int idx = tid; idx < PF_BK * CH; idx += PF_WARPS * 32) {
             const int row = idx / CH, chunk = idx % CH;
             const int key = kt + row;
-            const bool valid = key >= k_begin && key < k_end;
+            const bool valid = (key >= k_begin || key < keep) && key < k_end;
             size_t off = 0;
             if (valid) {
                 const int page = table[key / p.page_size];
@@ -188,8 +193,8 @@ prefill_attention_mma_kernel(const DecodeParams p) {
                 pf_ldsm4(q_s + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), qf[ks]);
             }
         }
-        const int kt = kt0 + t * PF_BK;
-        const bool warp_sees = wpos_hi >= kt && kt + PF_BK - 1 >= wlo_min;
+        const int kt = tile_start(t, nhead, kt0, PF_BK);
+        const bool warp_sees = wpos_hi >= kt && (kt + PF_BK - 1 >= wlo_min || kt < keep_raw);
         if (warp_sees) {
             const uint32_t kst = kv_s + (t & 1) * 2 * KV_BYTES, vst = kst + KV_BYTES;
             float s[PF_BK / 8][4];
@@ -212,15 +217,15 @@ prefill_attention_mma_kernel(const DecodeParams p) {
             }
             // mask (only tiles that touch the diagonal or the window's edge need one), online
             // softmax in base 2: p = 2^(s * scale_log2 - m), one FMA and one ex2 per score
-            const bool full = kt + PF_BK - 1 <= wpos_lo && kt >= wlo_max;
+            const bool full = kt + PF_BK - 1 <= wpos_lo && (kt >= wlo_max || kt + PF_BK <= keep_raw);
             if (!full) {
 #pragma unroll
                 for (int n = 0; n < PF_BK / 8; ++n)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = kt + n * 8 + (lane & 3) * 2 + e;
-                        const bool v0 = key <= qpos0 && key >= qlo0;
-                        const bool v1 = key <= qpos1 && key >= qlo1;
+                        const bool v0 = key <= qpos0 && (key >= qlo0 || key < keep_raw);
+                        const bool v1 = key <= qpos1 && (key >= qlo1 || key < keep_raw);
                         if (!v0) s[n][e] = -INFINITY;
                         if (!v1) s[n][2 + e] = -INFINITY;
                     }
@@ -296,21 +301,50 @@ prefill_attention_mma_kernel(const DecodeParams p) {
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
     const int c = (lane & 3) * 2;
+    // One row of the result: elements [n][e0], [n][e0 + 1] of every 8-column group n, times `inv`.  With
+    // out_table the values were turned by their positions before they were cached, and the row is turned
+    // back by the query's position `pos`; both numbers of a pair lie in this thread.
+    auto store_row = [&](bf16* dst, int e0, float inv, int pos) {
+        if (EXT && p.out_table) {
+            const float* cs = p.out_table + (size_t)pos * (D / 2) * 2;
+            if (p.out_pairing) {  // pairs (2 i, 2 i + 1)
+#pragma unroll
+                for (int n = 0; n < D / 8; ++n) {
+                    const float2 t = *reinterpret_cast<const float2*>(cs + (n * 8 + c));  // pair (n * 8 + c) / 2
+                    const float u = o[n][e0] * inv, w = o[n][e0 + 1] * inv;
+                    *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + c) =
+                        __floats2bfloat162_rn(u * t.x + w * t.y, w * t.x - u * t.y);
+                }
+            } else {  // pairs (i, i + D / 2)
+#pragma unroll
+                for (int n = 0; n < D / 16; ++n) {
+                    const float4 t = *reinterpret_cast<const float4*>(cs + 2 * (n * 8 + c));  // pairs n * 8 + c, + 1
+                    const float u0 = o[n][e0] * inv, u1 = o[n][e0 + 1] * inv;
+                    const float w0 = o[n + D / 16][e0] * inv, w1 = o[n + D / 16][e0 + 1] * inv;
+                    *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + c) =
+                        __floats2bfloat162_rn(u0 * t.x + w0 * t.y, u1 * t.z + w1 * t.w);
+                    *reinterpret_cast<__nv_bfloat162*>(dst + D / 2 + n * 8 + c) =
+                        __floats2bfloat162_rn(w0 * t.x - u0 * t.y, w1 * t.z - u1 * t.w);
+                }
+            }
+            return;
+        }
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n)
+            *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + c) =
+                __floats2bfloat162_rn(o[n][e0] * inv, o[n][e0 + 1] * inv);
+    };
     if (gr0 < nrows) {
         bf16* dst = p.out + ((size_t)(q0 + gr0 / G) * p.nh + hk * G + gr0 % G) * D;
         float inv = 1.0f / l0;
         if (EXT) inv = pf_finish(p, l0, m0, q0 + gr0 / G, hk * G + gr0 % G);
-#pragma unroll
-        for (int n = 0; n < D / 8; ++n)
-            *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + c) = __floats2bfloat162_rn(o[n][0] * inv, o[n][1] * inv);
+        store_row(dst, 0, inv, qpos0);
     }
     if (gr1 < nrows) {
         bf16* dst = p.out + ((size_t)(q0 + gr1 / G) * p.nh + hk * G + gr1 % G) * D;
         float inv = 1.0f / l1;
         if (EXT) inv = pf_finish(p, l1, m1, q0 + gr1 / G, hk * G + gr1 % G);
-#pragma unroll
-        for (int n = 0; n < D / 8; ++n)
-            *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + c) = __floats2bfloat162_rn(o[n][2] * inv, o[n][3] * inv);
+        store_row(dst, 2, inv, qpos1);
     }
 }
 

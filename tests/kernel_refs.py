@@ -484,7 +484,7 @@ def qk_prep(proj, num_heads, num_kv_heads, head_dim, positions, row_of_token, ta
     n, d, dv = proj.shape[0], head_dim, vcache.shape[3]
     nq, nk = num_heads * d, num_kv_heads * d
     pos = positions[:n].long()
-    q = proj[:, :nq].float().view(n, num_heads, d)
+    q = proj[:, :nq].float().view(n, num_heads, d).clone()
     k_raw = proj[:, nq:nq + nk]
     k = k_raw.float().view(n, num_kv_heads, d)
     v = k_raw if values_are_keys else proj[:, nq + nk:nq + nk + num_kv_heads * dv]
