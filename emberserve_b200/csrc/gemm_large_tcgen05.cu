@@ -57,6 +57,14 @@ struct GemmLargeParams {
     // dependency wait.  nullptr: one weight for all rows.
     const int* tile_expert = nullptr;
     int expert_rows = 0;
+    // GATED, grouped form: row r of x is the pair row_pair[r] (-1: a row between two experts) and both
+    // sums of the row are multiplied by pair_scale[pair] before the activation (nullptr: by 1).
+    const int* row_pair = nullptr;
+    const float* pair_scale = nullptr;
+    // act_capped: with g = min(gate, limit), u = clamp(up, -limit, limit) the result is
+    // g * sigmoid(alpha * g) * (u + 1) instead of silu(gate) * up
+    int act_capped = 0;
+    float act_limit = 0.f, act_alpha = 1.f;
 };
 
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
@@ -103,14 +111,31 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float silu_times(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float capped_glu(float g, float u, float scale, float limit, float alpha) {
+    g = fminf(g * scale, limit);
+    u = fminf(fmaxf(u * scale, -limit), limit);
+    return __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+}
 
 // One chunk of 32 accumulator columns of a token row to memory.  GATED: `a` = gate columns
 // [c0, c0+32), `b` = the up columns of the same outputs; else `a` = columns [c0, c0+32) of y.
 template <bool GATED>
 __device__ __forceinline__ void gl_store_chunk(const GemmLargeParams& p, int token, int n_tile, int c0,
-                                               const float (&a)[32], const float (&b)[32]) {
+                                               const float (&a)[32], const float (&b)[32], float scale) {
     if (token >= p.m_tok) return;
-    if (GATED) {
+    if (GATED && p.act_capped) {
+        bf16* dst = p.y + (size_t)token * p.n_out + (size_t)n_tile * GL_BN + c0;
+        const float lim = p.act_limit, al = p.act_alpha;
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(capped_glu(a[i], b[i], scale, lim, al), capped_glu(a[i + 1], b[i + 1], scale, lim, al));
+            o.y = pack_bf16x2(capped_glu(a[i + 2], b[i + 2], scale, lim, al), capped_glu(a[i + 3], b[i + 3], scale, lim, al));
+            o.z = pack_bf16x2(capped_glu(a[i + 4], b[i + 4], scale, lim, al), capped_glu(a[i + 5], b[i + 5], scale, lim, al));
+            o.w = pack_bf16x2(capped_glu(a[i + 6], b[i + 6], scale, lim, al), capped_glu(a[i + 7], b[i + 7], scale, lim, al));
+            *reinterpret_cast<uint4*>(dst + i) = o;
+        }
+    } else if (GATED) {
         bf16* dst = p.y + (size_t)token * p.n_out + (size_t)n_tile * GL_BN + c0;
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
@@ -300,6 +325,11 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
             if (!ok) break;
             tc_fence_after();
             const int token = m_tile * 2 * GL_BM + (int)rank * GL_BM + row_local;
+            float scale = 1.f;
+            if (GATED && p.pair_scale && token < p.m_tok) {
+                const int pr = p.row_pair[token];
+                scale = pr >= 0 ? p.pair_scale[pr] : 0.f;
+            }
             const uint32_t taddr = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)b * GL_ACC_COLS;
 #pragma unroll 1
             for (int c0 = c_begin; c0 < c_end; c0 += 32) {
@@ -310,7 +340,7 @@ gemm_large_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
                 float fa[32], fb[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) { fa[i] = __uint_as_float(ra[i]); fb[i] = GATED ? __uint_as_float(rb[i]) : 0.f; }
-                gl_store_chunk<GATED>(p, token, n_tile, c0, fa, fb);
+                gl_store_chunk<GATED>(p, token, n_tile, c0, fa, fb, scale);
             }
             tc_fence_before();
             __syncwarp();
@@ -409,9 +439,15 @@ EMS_EXPORT int ems_gemm_large_gated(const void* x, const void* w, void* act, int
 // pairs sorted by expert, every expert's rows starting at a multiple of 256; tile_expert[m] names the
 // expert of row tile m (-1: not in use); w: [experts, 2 * inter, k].  act[rows, inter] =
 // silu(gate) * up for the rows of tiles in use.  inter a multiple of 128, k a multiple of 8.
+// With pair_scale (float32, one number per pair) and row_pair (the pair of every row, -1 between
+// experts) both sums of a row are multiplied by its pair's number first; capped != 0 selects the
+// activation g * sigmoid(alpha * g) * (u + 1) of g = min(gate, limit), u = clamp(up, -limit, limit).
 EMS_EXPORT int ems_moe_up_grouped_tc05(const void* xs, const void* w, void* act, int rows, int inter, int k,
-                                       int experts, const int* tile_expert, cudaStream_t stream) {
+                                       int experts, const int* tile_expert, const int* row_pair,
+                                       const float* pair_scale, int capped, float limit, float alpha,
+                                       cudaStream_t stream) {
     if (rows <= 0 || inter <= 0) return EMS_OK;
+    if (pair_scale && !row_pair) return EMS_ERR_SHAPE;
     if (rows % (2 * GL_BM) || !ems_gemm_large_gated_supported(rows, inter, k) || experts <= 0) return EMS_ERR_SHAPE;
     if (((uintptr_t)xs % 16) || ((uintptr_t)w % 16) || ((uintptr_t)act % 16)) return EMS_ERR_ALIGN;
     int* status = tc_status_device_ptr();
@@ -427,6 +463,8 @@ EMS_EXPORT int ems_moe_up_grouped_tc05(const void* xs, const void* w, void* act,
     p.tiled = 0;
     p.tile_expert = tile_expert;
     p.expert_rows = 2 * inter;
+    p.row_pair = row_pair; p.pair_scale = pair_scale;
+    p.act_capped = capped ? 1 : 0; p.act_limit = limit; p.act_alpha = alpha;
     return launch_gemm_large<true>(mx, mw, p, stream);
 }
 

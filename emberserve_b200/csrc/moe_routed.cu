@@ -481,14 +481,17 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
     }
 }
 
-// out[t, :] = sum_k wts[t, k] * y[inv[t * top + k], :] for y in bfloat16 in the sorted layout
+// out[t, :] = sum_k wts[t, k] * y[inv[t * top + k], :] for y in bfloat16 in the sorted layout (wts may be
+// null: every weight 1), plus extra[t, :] (optional)
 __global__ void moe_combine_rows_kernel(const bf16* __restrict__ y, const int* __restrict__ inv,
-                                        const float* __restrict__ wts, bf16* __restrict__ out, int top, int H) {
+                                        const float* __restrict__ wts, bf16* __restrict__ out, int top, int H,
+                                        const bf16* __restrict__ extra) {
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k)
-            s = fmaf(wts[t * top + k], __bfloat162float(y[(size_t)inv[t * top + k] * H + c]), s);
+            s = fmaf(wts ? wts[t * top + k] : 1.f, __bfloat162float(y[(size_t)inv[t * top + k] * H + c]), s);
+        if (extra) s += __bfloat162float(extra[t * H + c]);
         out[t * H + c] = __float2bfloat16_rn(s);
     }
 }
@@ -498,11 +501,11 @@ __global__ void moe_combine_rows_kernel(const bf16* __restrict__ y, const int* _
 using namespace ems;
 
 EMS_EXPORT int ems_moe_combine_rows(const void* y, const int* inv, const float* wts, void* out, int n, int top, int H,
-                                    cudaStream_t stream) {
+                                    const void* extra, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     int th = 32;
     while (th < H && th < 256) th <<= 1;
-    moe_combine_rows_kernel<<<n, th, 0, stream>>>((const bf16*)y, inv, wts, (bf16*)out, top, H);
+    moe_combine_rows_kernel<<<n, th, 0, stream>>>((const bf16*)y, inv, wts, (bf16*)out, top, H, (const bf16*)extra);
     return launch_status();
 }
 

@@ -91,9 +91,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
         "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P, I, P],
         "ems_moe_down_grouped_tc05": [P, P, P, I, I, I, I, P, P],
-        "ems_moe_combine_rows": [P, P, P, P, I, I, I, P],
+        "ems_moe_combine_rows": [P, P, P, P, I, I, I, P, P],
         "ems_moe_gather": [P, P, I, I, I, P, P],
-        "ems_moe_up_grouped_tc05": [P, P, P, I, I, I, I, P, P],
+        "ems_moe_up_grouped_tc05": [P, P, P, I, I, I, I, P, P, P, I, F, F, P],
         "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P, F, F, P],
         "ems_moe_down": [P, P, I, P, P, I, I, I, P, I, P],
         "ems_moe_combine": [P, P, P, I, I, I, I, P, P],
@@ -533,20 +533,27 @@ def moe_gather(x: torch.Tensor, perm: torch.Tensor, top: int, xs: torch.Tensor) 
 
 
 def moe_up_grouped_tc05_supported(inter: int, k: int) -> bool:
-    """Whether the tcgen05 grouped gate/up product takes the sizes (SiLU only, bfloat16)."""
+    """Whether the tcgen05 grouped gate/up product takes the sizes (bfloat16; SiLU or the capped form)."""
     return inter % 128 == 0 and k % 8 == 0
 
 
-def moe_up_grouped_tc05(xs: torch.Tensor, wgu: torch.Tensor, big: torch.Tensor, out: torch.Tensor) -> None:
+def moe_up_grouped_tc05(xs: torch.Tensor, wgu: torch.Tensor, big: torch.Tensor, out: torch.Tensor,
+                        act: str = "silu", perm: torch.Tensor | None = None, in_scale: torch.Tensor | None = None,
+                        limit: float = 0.0, alpha: float = 1.0) -> None:
     """out[i, :] = silu(xs[i] Wg[e]^T) * (xs[i] Wu[e]^T) for the rows of every group of 256 sorted rows
     that `big` gives to an expert e (-1: the group is skipped): the two-SM tcgen05 kernel of prompt
-    steps in its grouped form.  xs: [len(big) * 256, K]; wgu: [E, 2 * ff, K]."""
+    steps in its grouped form.  xs: [len(big) * 256, K]; wgu: [E, 2 * ff, K].  `act` "swiglu_capped" takes
+    `limit` and `alpha` as in `moe_up`; with `in_scale` (float32, one number per pair) and `perm` (the pair
+    of every sorted row, -1 between experts) both 32-bit sums of a row are multiplied by its pair's number."""
     e, ff2, k = wgu.shape
     rows = xs.shape[0]
     assert rows == big.numel() * MOE_BIG_TILE_ROWS and xs.shape[1] == k and out.shape == (rows, ff2 // 2)
-    assert xs.dtype == wgu.dtype == out.dtype == torch.bfloat16
+    assert xs.dtype == wgu.dtype == out.dtype == torch.bfloat16 and act in ("silu", "swiglu_capped")
+    assert in_scale is None or (perm is not None and perm.numel() >= rows)
     _check(library().ems_moe_up_grouped_tc05(_ptr(xs, "xs"), _ptr(wgu, "wgu"), _ptr(out, "out"), rows, ff2 // 2, k,
-                                             e, _i32(big, "big"), _stream()), "moe_up_grouped_tc05")
+                                             e, _i32(big, "big"), None if in_scale is None else _i32(perm, "perm"),
+                                             _f32(in_scale, "in_scale"), 1 if act == "swiglu_capped" else 0,
+                                             float(limit), float(alpha), _stream()), "moe_up_grouped_tc05")
 
 
 def moe_up(x: torch.Tensor, wgu: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
@@ -587,13 +594,16 @@ def moe_down_grouped_tc05(act: torch.Tensor, wdown: torch.Tensor, big: torch.Ten
                                                _i32(big, "big"), _stream()), "moe_down_grouped_tc05")
 
 
-def moe_combine_rows(y: torch.Tensor, inv: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> None:
-    """out[t, :] = sum_k weights[t, k] * y[inv[t * top + k], :] (k ascending) for bfloat16 rows `y` in the
-    sorted layout."""
+def moe_combine_rows(y: torch.Tensor, inv: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor, top: int,
+                     extra: torch.Tensor | None = None) -> None:
+    """out[t, :] = sum_k weights[t, k] * y[inv[t * top + k], :] (k ascending; every weight 1 when `weights` is
+    None) + extra[t, :] (optional) for bfloat16 rows `y` in the sorted layout."""
     n, h = out.shape
-    assert y.dtype == out.dtype == torch.bfloat16 and weights.dtype == torch.float32 and y.shape[1] == h
+    assert y.dtype == out.dtype == torch.bfloat16 and y.shape[1] == h
+    assert weights is None or weights.dtype == torch.float32
+    assert extra is None or (extra.dtype == out.dtype and extra.shape == out.shape)
     _check(library().ems_moe_combine_rows(_ptr(y, "y"), _i32(inv, "inv"), _ptr(weights, "weights"), _ptr(out, "out"),
-                                          n, top, h, _stream()), "moe_combine_rows")
+                                          n, top, h, _ptr(extra, "extra"), _stream()), "moe_combine_rows")
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor, top: int,

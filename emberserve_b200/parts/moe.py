@@ -123,8 +123,8 @@ class RoutedGLU(FeedForward):
             extra = ctx.scratch("ffn_shared", (n, s.hidden), ctx.dtype)
             extra.copy_(self.shared_ffn.forward(x, ctx))
         scaled_in = weights if s.weight_on_input else None
-        if (x.is_cuda and ctx.dtype == torch.bfloat16 and n > _GROUPED_TC05_TOKENS and s.activation == "silu"
-                and not s.weight_on_input and extra is None and s.scoring == "softmax"
+        if (x.is_cuda and ctx.dtype == torch.bfloat16 and n > _GROUPED_TC05_TOKENS
+                and s.activation in ("silu", "swiglu_capped")
                 and K.moe_up_grouped_tc05_supported(s.intermediate, s.hidden)):
             big_rows = K.MOE_BIG_TILE_ROWS
             big = ctx.scratch("moe_big", (K.moe_max_tiles(pairs, e, big_rows),), torch.int32)
@@ -132,16 +132,16 @@ class RoutedGLU(FeedForward):
             perm = ctx.scratch("moe_perm", (rows,), torch.int32)
             inv = ctx.scratch("moe_inv", (pairs,), torch.int32)
             K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles, align=big_rows,
-                        big=big, inv=inv)
+                        big=big, inv=inv, scoring=s.scoring)
             xs = ctx.scratch("moe_xs", (rows, s.hidden), ctx.dtype)
             K.moe_gather(x, perm, top, xs)
             act = ctx.scratch("moe_act", (rows, s.intermediate), ctx.dtype)
-            K.moe_up_grouped_tc05(xs, wgu, big, act)
+            K.moe_up_grouped_tc05(xs, wgu, big, act, s.activation, perm, scaled_in, s.act_limit, s.act_alpha)
             if s.intermediate % 8 == 0 and s.hidden % 8 == 0:  # the down product in the same form
                 y16 = ctx.scratch("moe_y16", (rows, s.hidden), ctx.dtype)
                 K.moe_down_grouped_tc05(act, self.wdown.view(e, s.hidden, s.intermediate), big, y16)
                 out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
-                K.moe_combine_rows(y16, inv, weights, out, top)
+                K.moe_combine_rows(y16, inv, None if s.weight_on_input else weights, out, top, extra=extra)
                 return out
         else:
             perm = ctx.scratch("moe_perm", (pairs,), torch.int32)

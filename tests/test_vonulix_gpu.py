@@ -278,6 +278,47 @@ def test_sigmoid_scored_experts_whose_scores_multiply_their_inputs(dtype, n, e, 
     _close(got, want, dtype, "experts", tol16=2.5e-2)
 
 
+def test_experts_of_a_long_prompt_on_the_grouped_tensor_core_product():
+    """More than 512 tokens in bfloat16: the pairs are laid out in groups of 256 rows per expert, gathered,
+    and both products run in their grouped tcgen05 form, the scores on the 32-bit sums and the capped
+    activation in the first one's epilogue, a shared expert's rows added at the end."""
+    K = _K()
+    g = torch.Generator().manual_seed(12)
+    for n, e, top, hid, ff, limit in ((700, 5, 2, 64, 128, 1.5), (1500, 16, 1, 192, 256, 2.0), (520, 3, 3, 128, 128, 0.6)):
+        x = torch.randn(n, hid, generator=g).to(torch.bfloat16)
+        w = {"router": (torch.randn(e, hid, generator=g) * 0.3).to(torch.bfloat16)}
+        for j in range(e):
+            w[f"e{j}.gate"] = (torch.randn(ff, hid, generator=g) * 1.5 / math.sqrt(hid)).to(torch.bfloat16)
+            w[f"e{j}.up"] = (torch.randn(ff, hid, generator=g) * 1.5 / math.sqrt(hid)).to(torch.bfloat16)
+            w[f"e{j}.down"] = (torch.randn(hid, ff, generator=g) / math.sqrt(ff)).to(torch.bfloat16)
+        wgu = torch.stack([torch.cat((w[f"e{j}.gate"], w[f"e{j}.up"])) for j in range(e)]).to(DEV)
+        wdown = torch.stack([w[f"e{j}.down"] for j in range(e)]).to(DEV)
+        extra = torch.randn(n, hid, generator=g).to(torch.bfloat16)
+        xd, pairs = x.to(DEV), n * top
+        logits = xd.float() @ w["router"].to(DEV).float().t()
+        tiles = K.moe_max_tiles(pairs, e, K.moe_tile_rows())
+        big = torch.zeros(K.moe_max_tiles(pairs, e, K.MOE_BIG_TILE_ROWS), dtype=torch.int32, device=DEV)
+        rows = big.numel() * K.MOE_BIG_TILE_ROWS
+        ids, inv = (torch.zeros(pairs, dtype=torch.int32, device=DEV) for _ in range(2))
+        perm = torch.zeros(rows, dtype=torch.int32, device=DEV)
+        weights = torch.zeros(pairs, device=DEV)
+        offsets = torch.zeros(3 * e + 1, dtype=torch.int32, device=DEV)
+        plan = torch.zeros(1 + 3 * tiles, dtype=torch.int32, device=DEV)
+        K.moe_route(logits, top, False, ids, weights, offsets, perm, plan, tiles, align=K.MOE_BIG_TILE_ROWS, big=big,
+                    inv=inv, scoring="sigmoid")
+        xs = torch.zeros(rows, hid, dtype=torch.bfloat16, device=DEV)
+        K.moe_gather(xd, perm, top, xs)
+        act = torch.zeros(rows, ff, dtype=torch.bfloat16, device=DEV)
+        K.moe_up_grouped_tc05(xs, wgu, big, act, "swiglu_capped", perm, weights, limit, 1.702)
+        y16 = torch.zeros(rows, hid, dtype=torch.bfloat16, device=DEV)
+        K.moe_down_grouped_tc05(act, wdown, big, y16)
+        out = torch.zeros(n, hid, dtype=torch.bfloat16, device=DEV)
+        K.moe_combine_rows(y16, inv, None, out, top, extra=extra.to(DEV))
+        m = {"router": {"experts": e, "top": top}, "expert": {"limit": limit}}
+        want = plain.routed_experts(x.double(), {k: v.double() for k, v in w.items()}, "", m) + extra.double()
+        _close(out, want, torch.bfloat16, f"{n} tokens, {e} experts", tol16=2.5e-2)
+
+
 @DTYPES
 def test_capped_activation_and_the_gate_per_token(dtype):
     """g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1); with the row's
@@ -478,6 +519,24 @@ def test_tensor_core_head_sizes_against_plain_and_against_the_generic_kernel(tmp
     generic = _replay(model, None, torch.bfloat16, steps, page_size=16, attn_kernel="generic")
     errs = np.array([float(np.abs(got[k] - generic[k]).max()) for k in got]) / scale
     assert errs.max() <= TOL16 / 2 and np.median(errs) <= TOL16 / 8, f"{cut}: {errs.max():.3e} {np.median(errs):.3e}"
+
+
+def test_a_long_prompt_whole_and_in_portions(tmp_path):
+    """A prompt of 900 tokens in one step (the experts on the grouped tensor-core products, attention over
+    many key tiles, kept keys far behind the window) against the plain implementation and against the
+    same prompt in portions of at most 300 tokens."""
+    cfg = json.loads(json.dumps(VON_T))
+    cfg["layers"][0]["mlp"] = tv._moe(6, 2, 128, 2.0, (128, 1.0))
+    cfg["layers"][2]["mlp"] = tv._moe(5, 1, 256, 1.0)
+    model = tv.write_model(cfg, tmp_path / "long", 41)
+    reqs = rc.make_requests(cfg["vocab"], [900], seed=17)
+    want = _oracle(model, reqs)
+    scale = float(np.abs(want["r0"]).max())
+    whole = _replay(model, None, torch.bfloat16, rc.whole(reqs), page_size=16)
+    _compare(whole, want, reqs, scale, torch.bfloat16, "whole")
+    cut = _replay(model, None, torch.bfloat16, rc.portions(reqs, (300, 129, 2, 270, 199)), page_size=16)
+    _compare(cut, want, reqs, scale, torch.bfloat16, "portions")
+    _compare(_replay(model, None, torch.float32, rc.whole(reqs), page_size=16), want, reqs, scale, torch.float32, "fp32")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
