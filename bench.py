@@ -1019,7 +1019,7 @@ def run_vonulix(args) -> dict:
     from emberserve_b200.config.vonulix import VonulixConfig
 
     z = VONULIX_SIZES[args.vonulix_size]
-    von = VonulixConfig.from_dict(vonulix_config(args.vonulix_size))
+    von = VonulixConfig.from_dict(vonulix_config(args.vonulix_size, layers=args.layers or 6))
     runs = len(von.layers)
     qwen = Qwen2Config.from_dict(dict(
         SHAPE_7B, vocab_size=32000, hidden_size=z["width"], num_attention_heads=z["heads"],
