@@ -44,7 +44,19 @@ __global__ void token_gate_kernel(const T* __restrict__ z, const void* __restric
     }
 }
 
-template <typename T>
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
+}
+
+// VEC4: H and the plane are multiples of 4 and every pointer is aligned for four elements
+template <typename T, bool VEC4>
 __global__ void depth_mix_kernel(const T* __restrict__ delta, const void* __restrict__ gain, int g_dtype, float eps,
                                  float* __restrict__ residual, float* __restrict__ hist, const float* __restrict__ w,
                                  int count, size_t plane, int H) {
@@ -62,6 +74,40 @@ __global__ void depth_mix_kernel(const T* __restrict__ delta, const void* __rest
         f = 1.0f / sqrtf(block_sum(ss, red) / (float)H + eps);
     }
     float* newest = hist + (size_t)(count - 1) * plane + n * H;
+    if (VEC4) {
+        // four columns per thread, the earlier states' loads of a column group in flight together; the
+        // sums run over the depths in index order as in the scalar form below
+        const float* hrow = hist + n * H;
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 x = *reinterpret_cast<const float4*>(r + i);
+            if (d) {
+                float dv[4];
+                load4<T>(d + i, dv);
+                if (gain) {
+                    x.x += dv[0] * f * load_any(gain, g_dtype, i);
+                    x.y += dv[1] * f * load_any(gain, g_dtype, i + 1);
+                    x.z += dv[2] * f * load_any(gain, g_dtype, i + 2);
+                    x.w += dv[3] * f * load_any(gain, g_dtype, i + 3);
+                } else {
+                    x.x += dv[0]; x.y += dv[1]; x.z += dv[2]; x.w += dv[3];
+                }
+            }
+            *reinterpret_cast<float4*>(newest + i) = x;
+            if (w) {
+                float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                for (int j = 0; j + 1 < count; ++j) {
+                    const float4 h = *reinterpret_cast<const float4*>(hrow + (size_t)j * plane + i);
+                    const float wj = w[j];
+                    s.x = fmaf(wj, h.x, s.x); s.y = fmaf(wj, h.y, s.y); s.z = fmaf(wj, h.z, s.z); s.w = fmaf(wj, h.w, s.w);
+                }
+                const float wl = w[count - 1];
+                x.x = fmaf(wl, x.x, s.x); x.y = fmaf(wl, x.y, s.y); x.z = fmaf(wl, x.z, s.z); x.w = fmaf(wl, x.w, s.w);
+            }
+            *reinterpret_cast<float4*>(r + i) = x;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float x = r[i];
         if (d) x += gain ? to_f32<T>(d[i]) * f * load_any(gain, g_dtype, i) : to_f32<T>(d[i]);
@@ -114,13 +160,16 @@ EMS_EXPORT int ems_depth_mix(const void* delta, const void* gain, int g_dtype, f
                              const float* w, int count, long long plane, int dtype, int n, int H, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     if (count < 1 || plane < (long long)n * H) return EMS_ERR_SHAPE;
-    const int th = depth_threads(H);
-    if (dtype == EMS_F32)
-        depth_mix_kernel<float><<<n, th, 0, stream>>>((const float*)delta, gain, g_dtype, eps, residual, hist, w, count,
-                                                      (size_t)plane, H);
-    else if (dtype == EMS_BF16)
-        depth_mix_kernel<bf16><<<n, th, 0, stream>>>((const bf16*)delta, gain, g_dtype, eps, residual, hist, w, count,
-                                                     (size_t)plane, H);
+    const bool vec = H % 4 == 0 && plane % 4 == 0 && ((uintptr_t)residual % 16) == 0 && ((uintptr_t)hist % 16) == 0 &&
+                     ((uintptr_t)delta % 16) == 0;
+    const int th = depth_threads(vec ? H / 4 : H);
+    if (dtype == EMS_F32) {
+        auto k = vec ? depth_mix_kernel<float, true> : depth_mix_kernel<float, false>;
+        k<<<n, th, 0, stream>>>((const float*)delta, gain, g_dtype, eps, residual, hist, w, count, (size_t)plane, H);
+    } else if (dtype == EMS_BF16) {
+        auto k = vec ? depth_mix_kernel<bf16, true> : depth_mix_kernel<bf16, false>;
+        k<<<n, th, 0, stream>>>((const bf16*)delta, gain, g_dtype, eps, residual, hist, w, count, (size_t)plane, H);
+    }
     else return EMS_ERR_DTYPE;
     return launch_status();
 }

@@ -347,6 +347,18 @@ def test_token_input_and_depth_average_kernels(dtype):
     got = torch.empty(n, c, dtype=dtype, device=DEV)
     _K().token_gate(z.to(DEV), table.to(DEV), 2 * c, tokens.to(torch.int32).to(DEV), got)
     _close(got, plain.gelu_tanh(z.double()) * table[tokens][:, 2 * c:3 * c].double(), dtype, "token gate")
+    for h in (40, 42, 2048):  # four columns per thread where the width allows, one otherwise
+        _depth_average_case(g, dtype, n, h, depths)
+    # the stream itself as an operand: the add in 32 bits, rounded once
+    res = torch.randn(n, h, generator=g)
+    delta = torch.randn(n, h, generator=g).to(dtype)
+    dr, xb = res.to(DEV), torch.empty(n, h, dtype=dtype, device=DEV)
+    _K().add_cast(delta.to(DEV), dr, xb)
+    _close(dr, res.double() + delta.double(), torch.float32, "sum")
+    assert torch.equal(xb.cpu(), (res + delta.float()).to(dtype))
+
+
+def _depth_average_case(g, dtype, n, h, depths):
     hist = torch.randn(depths + 1, n, h, generator=g)
     res = torch.randn(n, h, generator=g)
     for count, normed in ((1, False), (2, True), (3, False), (5, True)):
@@ -364,12 +376,6 @@ def test_token_input_and_depth_average_kernels(dtype):
         _close(dr, want, torch.float32, f"depth {count}")
         _close(dh[count - 1], x, torch.float32, f"state {count}")
         assert torch.equal(dh[:count - 1].cpu(), hist[:count - 1]) and torch.equal(dh[count:].cpu(), hist[count:])
-    # the stream itself as an operand: the add in 32 bits, rounded once
-    delta = torch.randn(n, h, generator=g).to(dtype)
-    dr, xb = res.to(DEV), torch.empty(n, h, dtype=dtype, device=DEV)
-    _K().add_cast(delta.to(DEV), dr, xb)
-    _close(dr, res.double() + delta.double(), torch.float32, "sum")
-    assert torch.equal(xb.cpu(), (res + delta.float()).to(dtype))
 
 
 # ---- the engine -------------------------------------------------------------------------------
