@@ -143,7 +143,8 @@ def _run_attention(case, nh, nkv, d, scale, max_q, rows, window, keep, table, us
 
 ATTENTION_SIZES = [(6, 2, 8, 16, 4, 7, 3), (4, 4, 16, 8, 16, 40, 11), (5, 1, 24, 24, 8, 1, 9), (2, 1, 24, 32, 16, None, 0),
                    (8, 2, 8, 8, 16, 16, 16), (6, 2, 64, 64, 16, 40, 5), (3, 3, 128, 128, 32, 100, 70),
-                   (8, 1, 64, 64, 8, 33, 64), (4, 2, 64, 64, 16, 64, 1), (2, 2, 64, 32, 16, 20, 4)]
+                   (8, 1, 64, 64, 8, 33, 64), (4, 2, 64, 64, 16, 64, 1), (2, 2, 64, 32, 16, 20, 4),
+                   (32, 1, 64, 64, 16, 50, 6), (2, 2, 96, 32, 16, 30, 2), (1, 1, 256, 256, 16, 130, 3)]
 
 
 @DTYPES
@@ -257,7 +258,8 @@ def _route_and_run(x, router, wgu, wdown, top, limit, dtype):
 
 @DTYPES
 @pytest.mark.parametrize("n,e,top,hid,ff,limit", [(37, 5, 2, 48, 24, 1.5), (1, 16, 1, 64, 96, 2.0), (200, 9, 1, 40, 8, 0.7),
-                                                  (70, 6, 4, 40, 12, 4.0), (130, 3, 3, 64, 32, 2.5), (600, 8, 2, 128, 64, 1.0)])
+                                                  (70, 6, 4, 40, 12, 4.0), (130, 3, 3, 64, 32, 2.5), (600, 8, 2, 128, 64, 1.0),
+                                                  (50, 1, 1, 32, 16, 1.0), (9, 2, 1, 36, 20, 3.0)])
 def test_sigmoid_scored_experts_whose_scores_multiply_their_inputs(dtype, n, e, top, hid, ff, limit):
     g = torch.Generator().manual_seed(n + e)
     x = torch.randn(n, hid, generator=g).to(dtype)
