@@ -142,7 +142,7 @@ def _run_attention(case, nh, nkv, d, scale, max_q, rows, window, keep, table, us
 
 
 ATTENTION_SIZES = [(6, 2, 8, 16, 4, 7, 3), (4, 4, 16, 8, 16, 40, 11), (5, 1, 24, 24, 8, 1, 9), (2, 1, 24, 32, 16, None, 0),
-                   (8, 2, 8, 8, 16, 16, 16), (6, 2, 64, 64, 16, 40, 5), (3, 3, 128, 128, 32, 100, 70),
+                   (8, 2, 8, 8, 16, 16, 16), (9, 3, 64, 64, 16, 40, 5), (3, 3, 128, 128, 32, 100, 70),
                    (8, 1, 64, 64, 8, 33, 64), (4, 2, 64, 64, 16, 64, 1), (2, 2, 64, 32, 16, 20, 4),
                    (32, 1, 64, 64, 16, 50, 6), (2, 2, 96, 32, 16, 30, 2), (1, 1, 256, 256, 16, 130, 3)]
 
@@ -257,7 +257,7 @@ def _route_and_run(x, router, wgu, wdown, top, limit, dtype):
 
 
 @DTYPES
-@pytest.mark.parametrize("n,e,top,hid,ff,limit", [(37, 5, 2, 48, 24, 1.5), (1, 16, 1, 64, 96, 2.0), (200, 9, 1, 40, 8, 0.7),
+@pytest.mark.parametrize("n,e,top,hid,ff,limit", [(37, 5, 2, 48, 24, 1.5), (1, 12, 1, 64, 80, 2.2), (200, 9, 1, 40, 8, 0.7),
                                                   (70, 6, 4, 40, 12, 4.0), (130, 3, 3, 64, 32, 2.5), (600, 8, 2, 128, 64, 1.0),
                                                   (50, 1, 1, 32, 16, 1.0), (9, 2, 1, 36, 20, 3.0)])
 def test_sigmoid_scored_experts_whose_scores_multiply_their_inputs(dtype, n, e, top, hid, ff, limit):
@@ -326,7 +326,7 @@ def test_capped_activation_and_the_gate_per_token(dtype):
     """g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1); with the row's
     own sigmoid number (the shared expert's gate) on top.  Inputs reach well past the limits."""
     g = torch.Generator().manual_seed(3)
-    for i, limit in ((24, 0.8), (96, 1.0), (40, 7.0)):
+    for i, limit in ((24, 0.8), (88, 1.1), (40, 7.0)):
         gu = (3 * torch.randn(19, 2 * i + 8, generator=g)).to(dtype)
         a, b = gu[:, :i].double().clamp(max=limit), gu[:, i:2 * i].double().clamp(-limit, limit)
         want = a * torch.sigmoid(1.702 * a) * (b + 1)
@@ -426,7 +426,7 @@ def _compare(got, want, reqs, scale, dtype, what):
 # and the token input and the depth average around the smallest layer
 ONE_LAYER = {
     "attention": (tv._layer(tv._mixer(4, 2, 16, 8, 9, 2, 8, 1000.0, 2.0), None), None),
-    "attention_64": (tv._layer(tv._mixer(6, 2, 64, 64, 20, 5, 32, 5000.0, 4.0), None), None),
+    "attention_64": (tv._layer(tv._mixer(4, 2, 64, 64, 20, 5, 16, 5000.0, 2.0), None), None),
     "attention_128": (tv._layer(tv._mixer(2, 1, 128, 128, 70, 17, 128, 5000.0), None), None),
     "attention_unbounded": (tv._layer(tv._mixer(3, 1, 64, 64, None, 0, 16, 100.0), None), None),
     "experts": (tv._layer(tv._mixer(1, 1, 8, 8, None, 0, 0, 10.0), tv._moe(7, 2, 16, 1.2)), None),
@@ -505,7 +505,7 @@ VON_T = {
     "architecture": "Vonulix", "vocab": 120, "width": 64, "norm": {"eps": 1e-6}, "max_positions": 1024,
     "embedding": {"scale": 4.0}, "token_side": {"dim": 8},
     "layers": [
-        tv._layer(tv._mixer(6, 1, 64, 64, 90, 7, 32, 50000.0, 4.0, 0.2), tv._moe(6, 2, 32, 2.0, (32, 1.0))),
+        tv._layer(tv._mixer(6, 1, 64, 64, 90, 7, 48, 30000.0, 3.0, 0.2), tv._moe(6, 2, 32, 2.0, (32, 1.0))),
         tv._layer(tv._mixer(2, 2, 128, 128, 150, 70, 64, 10000.0), None),
         tv._layer(tv._mixer(4, 2, 64, 64, 33, 0, 64, 100.0, 2.0), tv._moe(5, 1, 48, 1.0)),
     ],
