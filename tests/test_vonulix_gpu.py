@@ -526,7 +526,9 @@ def test_tensor_core_head_sizes_against_plain_and_against_the_generic_kernel(tmp
     _compare(got, want, reqs, scale, torch.bfloat16, f"bfloat16 {cut}")
     generic = _replay(model, None, torch.bfloat16, steps, page_size=16, attn_kernel="generic")
     errs = np.array([float(np.abs(got[k] - generic[k]).max()) for k in got]) / scale
-    assert errs.max() <= TOL16 / 2 and np.median(errs) <= TOL16 / 8, f"{cut}: {errs.max():.3e} {np.median(errs):.3e}"
+    # (two bfloat16 runs may choose another expert where two scores nearly tie, as in `_compare`)
+    over = int((errs > TOL16 / 2).sum())
+    assert over <= max(1, len(errs) // 50) and np.median(errs) <= TOL16 / 8, f"{cut}: {over} over, {errs.max():.3e} {np.median(errs):.3e}"
 
 
 def test_a_long_prompt_whole_and_in_portions(tmp_path):
