@@ -67,8 +67,10 @@ __device__ __forceinline__ float pf_finish(const DecodeParams& p, float l, float
     return inv;
 }
 
-// EXT: the kernel also honours DecodeParams::chunk, sinks and gate, and feeds the softmax weights to
-// the second product as value + remainder (two bfloat16 terms).
+// EXT: the kernel also honours DecodeParams::chunk, sinks, gate, keep (first keys that stay visible beside
+// the window: their tiles are walked before the window's) and out_table (the result is turned back by the
+// query's position in the epilogue), and feeds the softmax weights to the second product as value +
+// remainder (two bfloat16 terms).
 template <int D, bool PAGE16, bool EXT = false>
 __global__ void __launch_bounds__(PF_WARPS * 32)
 prefill_attention_mma_kernel(const DecodeParams p) {
