@@ -39,10 +39,17 @@ class ModelConfig:
     ``architectures`` entry it serves and parses that architecture's keys."""
 
     architecture: ClassVar[str] = ""
+    # True: some size of the design is given by a tensor's shape only; `load_config` then hands the
+    # checkpoint's tensor shapes to `with_tensor_shapes`
+    wants_tensor_shapes: ClassVar[bool] = False
 
     @classmethod
     def from_dict(cls, cfg: dict[str, Any]) -> "ModelConfig":
         raise NotImplementedError
+
+    def with_tensor_shapes(self, shapes: "dict[str, tuple[int, ...]]") -> "ModelConfig":
+        """The configuration completed by sizes that only the checkpoint's tensors give (name -> shape)."""
+        return self
 
     def to_dict(self) -> dict[str, Any]:
         raise NotImplementedError

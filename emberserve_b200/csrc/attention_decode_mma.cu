@@ -84,7 +84,7 @@ decode_attention_mma_kernel(const DecodeParams p) {
     const int tok = p.cu_q[b];
     const int ctx = p.starts[b] + 1;           // keys visible to the query: [k_begin, ctx)
     const int k_begin = first_visible(ctx - 1, p.window, p.chunk);
-    const bool ext = p.chunk > 0 || p.sinks != nullptr || p.gate != nullptr;  // then the weights keep 16 bits (see below)
+    const bool ext = p.chunk > 0 || p.sinks != nullptr || p.gate != nullptr || p.softcap > 0.f;  // then the weights keep 16 bits (see below)
     const int G = p.G;
 
     // this block's tiles (16 keys each, aligned to absolute positions), and this warp's
@@ -269,6 +269,13 @@ decode_attention_mma_kernel(const DecodeParams p) {
                 mma_bf16_16816(s[0], qf[ks], bfrag[0], bfrag[1]);
                 mma_bf16_16816(s[1], qf[ks], bfrag[2], bfrag[3]);
             }
+        }
+        if (p.softcap > 0.f) {   // capped scores, kept in units of 1 / scale so that what follows is unchanged
+            const float c2 = p.scale / p.softcap, c1 = p.softcap / p.scale;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[n][e] = c1 * tanhf(s[n][e] * c2);
         }
         // softmax of the tile, rows r0 (values [n][0..1]) and r1 (values [n][2..3]), in base 2:
         // p = 2^(s * scale_log2 - m), one FMA and one ex2 per score

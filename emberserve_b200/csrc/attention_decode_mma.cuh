@@ -35,6 +35,8 @@ struct DecodeParams {
     const float* out_table = nullptr;  // [positions, D / 2, (cos, sin)]: the result is turned back by the query's position
     int out_pairing = 0;            // 0: pair (i, i + D / 2); 1: pair (2 i, 2 i + 1)
     const int* positions = nullptr; // [N] position of each token of the step
+    float softcap = 0.f;            // > 0: a score s (already scaled) becomes softcap * tanh(s / softcap)
+    float scale = 0.f;              // the plain score scale (scale_log2 / log2(e)), read with softcap
 };
 
 // The key tiles that a block walks when the first `keep` keys stay visible beside the window: `nhead`

@@ -50,6 +50,7 @@ struct AttnParams {
     const float* out_table = nullptr;
     int out_pairing = 0;
     const int* positions = nullptr; // [N] position of every token of the step (for the merge of key splits)
+    float softcap = 0.f;            // > 0: a scaled score s becomes softcap * tanh(s / softcap) before the softmax
 };
 
 template <typename T, int VEC> struct VecLoad;
@@ -187,7 +188,8 @@ paged_attention_kernel(const AttnParams p) {
 #pragma unroll
         for (int r = 0; r < RPW; ++r) {
             const bool visible = key <= qpos[r] && (key >= qlo[r] || key < p.keep);
-            const float s = visible ? acc[r] * p.scale : -INFINITY;
+            float s = -INFINITY;
+            if (visible) s = p.softcap > 0.f ? p.softcap * tanhf(acc[r] * p.scale / p.softcap) : acc[r] * p.scale;
             const float m_new = fmaxf(m[r], warp_max(s));
             const float pe = visible ? expf(s - m_new) : 0.f;
             const float alpha = m_new == -INFINITY ? 1.f : expf(m[r] - m_new);
@@ -387,7 +389,7 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
                                int max_q_len, int splits, void* scratch, long long scratch_bytes,
                                int impl, int chunk, const float* sinks, const void* gate, long long gate_stride,
                                int keep, int DV, const float* out_table, int out_pairing, const int* positions,
-                               cudaStream_t stream) {
+                               float softcap, cudaStream_t stream) {
     // impl: 0 = the fastest kernel that takes the case, 1 = the generic kernel, 2 = the
     // tcgen05 prompt kernel or an error, 3 = the mma.sync kernels where they take the case.
     if (B <= 0 || N <= 0) return EMS_OK;
@@ -400,7 +402,7 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
         return EMS_ERR_SHAPE;
     if (window <= 0 && chunk <= 0) keep = 0;  // every key is visible anyway
     // the tensor-core kernels know the plain causal form (and a window)
-    const bool plain = chunk <= 0 && !sinks && !gate && keep == 0 && DV == D && !out_table;
+    const bool plain = chunk <= 0 && !sinks && !gate && keep == 0 && DV == D && !out_table && !(softcap > 0.f);
     if (!plain && impl == 2) return EMS_ERR_SHAPE;
     if ((q_stride * esize) % 16 || ((uintptr_t)q % 16) || ((uintptr_t)kcache % 16) || ((uintptr_t)vcache % 16))
         return EMS_ERR_ALIGN;
@@ -411,6 +413,7 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
     p.scale = scale; p.part_o = nullptr; p.part_ml = nullptr;
     p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_stride = gate_stride;
     p.keep = keep; p.DV = DV; p.out_table = out_table; p.out_pairing = out_pairing; p.positions = positions;
+    p.softcap = softcap > 0.f ? softcap : 0.f;
     if (splits > 1) {
         if (scratch == nullptr || scratch_bytes < ems_paged_attention_scratch_bytes(N, nh, DV, splits))
             return EMS_ERR_SCRATCH;
@@ -426,6 +429,7 @@ static int paged_attention_any(const void* q, long long q_stride, void* out, int
     d.scale_log2 = scale * 1.4426950408889634f;
     d.chunk = chunk; d.sinks = sinks; d.gate = reinterpret_cast<const bf16*>(gate); d.gate_stride = gate_stride;
     d.keep = keep; d.out_table = out_table; d.out_pairing = out_pairing; d.positions = positions;
+    d.softcap = p.softcap; d.scale = scale;
     if (!plain) {
         // prompt portions on the tensor cores where the sizes allow; everything else on the generic kernel
         const bool mma_form = DV == D;
@@ -482,7 +486,7 @@ EMS_EXPORT int ems_paged_attention(const void* q, long long q_stride, void* out,
                                    int impl, cudaStream_t stream) {
     return paged_attention_any(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride, page_size, cu_q,
                                starts, B, N, nh, nkv, D, window, scale, max_q_len, splits, scratch, scratch_bytes,
-                               impl, 0, nullptr, nullptr, 0, 0, D, nullptr, 0, nullptr, stream);
+                               impl, 0, nullptr, nullptr, 0, 0, D, nullptr, 0, nullptr, 0.f, stream);
 }
 
 // The same with a chunk mask, a sink per head in the softmax's denominator, a sigmoid gate per
@@ -497,11 +501,11 @@ EMS_EXPORT int ems_paged_attention_masked(const void* q, long long q_stride, voi
                                           const float* sinks, const void* gate, long long gate_stride, float scale,
                                           int max_q_len, int splits, void* scratch, long long scratch_bytes,
                                           int impl, int keep, int DV, const float* out_table, int out_pairing,
-                                          const int* positions, cudaStream_t stream) {
+                                          const int* positions, float softcap, cudaStream_t stream) {
     return paged_attention_any(q, q_stride, out, dtype, kcache, vcache, block_tables, bt_stride, page_size, cu_q,
                                starts, B, N, nh, nkv, D, window, scale, max_q_len, splits, scratch, scratch_bytes,
                                impl, chunk, sinks, gate, gate_stride, keep, DV, out_table, out_pairing, positions,
-                               stream);
+                               softcap, stream);
 }
 
 // ---------------------------------------------------------------------------------------

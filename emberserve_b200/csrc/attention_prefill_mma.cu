@@ -217,6 +217,13 @@ prefill_attention_mma_kernel(const DecodeParams p) {
                     }
                 }
             }
+            if (EXT && p.softcap > 0.f) {   // capped scores, kept in units of 1 / scale so that what follows is unchanged
+                const float c2 = p.scale / p.softcap, c1 = p.softcap / p.scale;
+#pragma unroll
+                for (int n = 0; n < PF_BK / 8; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[n][e] = c1 * tanhf(s[n][e] * c2);
+            }
             // mask (only tiles that touch the diagonal or the window's edge need one), online
             // softmax in base 2: p = 2^(s * scale_log2 - m), one FMA and one ex2 per score
             const bool full = kt + PF_BK - 1 <= wpos_lo && (kt >= wlo_max || kt + PF_BK <= keep_raw);

@@ -1,0 +1,487 @@
+// Kernels of layers whose two sub-layers read the same normed stream, of the delta-rule memory, and of a
+// selective state space:
+//
+//  * ems_add_scaled_norm2: residual += sum_i scale_i * delta_i (up to three deltas, 32-bit sum), then
+//    one root mean square of the new residual serves two norms with gains of their own (a block whose
+//    mixer and feed-forward both read norm(x)); every part is optional;
+//  * ems_stream_norm: the 32-bit stream itself is RMS-normed in place (a norm behind the embedding);
+//  * ems_softcap: x <- cap * tanh(x / cap) on 32-bit values (logits);
+//  * ems_delta_recurrence: a matrix memory per head written by the delta rule with a decay per key
+//    channel, S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//    (Schlag, Irie, Schmidhuber, "Linear Transformers Are Secretly Fast Weight Programmers", with the
+//    gate of Yang, Kautz, Hatamizadeh, "Gated Delta Networks: Improving Mamba2 with Delta Rule", taken
+//    per channel);
+//  * ems_ssm_gates: step size and decay of a selective state space with a scalar decay per head
+//    (Dao, Gu, "Transformers are SSMs: Generalized Models and Efficient Algorithms Through Structured
+//    State Space Duality"): dt = softplus(x + bias), a = exp(-exp(A_log) dt), b = dt;
+//  * ems_gate_group_norm: what follows that state space's read: (o + D_h act(x)) * silu(z), then an
+//    RMS norm in equal groups with a gain.
+//
+// States, decays, gates, unit norms and every product with a state are 32-bit; projections and
+// convolution outputs arrive in the activation type and are widened once.  A request's tokens are
+// walked in order by the same code in prompts, portions and single tokens.
+#include "common.cuh"
+
+namespace ems {
+
+__device__ __forceinline__ float d_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float d_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float d_silu(float z) { return z / (1.f + expf(-z)); }
+
+// ---------------------------------------------------------------------------------------
+// residual += s0 d0 + s1 d1 + s2 d2;  r = rsqrt(mean(residual^2) + eps);  out1 = residual r g1;  out2 = residual r g2
+// (gains are read as stored plus `gain_offset`).  With `rows` only those rows are normed, compactly, after
+// the sum went into every row.
+
+template <typename T>
+__global__ void add_scaled_norm2_kernel(const T* __restrict__ d0, const T* __restrict__ d1, const T* __restrict__ d2,
+                                        float s0, float s1, float s2, float* __restrict__ residual,
+                                        const void* __restrict__ g1, const void* __restrict__ g2, int g_dtype,
+                                        float gain_offset, float eps, T* __restrict__ out1, T* __restrict__ out2,
+                                        int C) {
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * C;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float x = residual[base + c];
+        if (d0 || d1 || d2) {
+            if (d0) x = fmaf(s0, to_f32<T>(d0[base + c]), x);
+            if (d1) x = fmaf(s1, to_f32<T>(d1[base + c]), x);
+            if (d2) x = fmaf(s2, to_f32<T>(d2[base + c]), x);
+            residual[base + c] = x;
+        }
+        ss = fmaf(x, x, ss);
+    }
+    if (!out1 && !out2) return;
+    const float r = rsqrtf(block_sum(ss, red) / C + eps);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float x = residual[base + c] * r;  // (this thread wrote it)
+        if (out1) out1[base + c] = from_f32<T>(x * (load_any(g1, g_dtype, c) + gain_offset));
+        if (out2) out2[base + c] = from_f32<T>(x * (load_any(g2, g_dtype, c) + gain_offset));
+    }
+}
+
+__global__ void stream_norm_kernel(float* __restrict__ residual, const void* __restrict__ gain, int g_dtype,
+                                   float gain_offset, float eps, int C) {
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * C;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) ss = fmaf(residual[base + c], residual[base + c], ss);
+    const float r = rsqrtf(block_sum(ss, red) / C + eps);
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+        residual[base + c] = residual[base + c] * r * (load_any(gain, g_dtype, c) + gain_offset);
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+}
+
+// ---------------------------------------------------------------------------------------
+// the delta-rule memory
+//
+// As in the matrix memory of recurrent.cu, a block of 16 warps owns a group of columns of one head's S
+// ([D, V]) for one request; a column is shared by SL lanes, lane s holding rows i * 4 SL + 4 s + e of
+// the column in registers.  Per tile of 32 tokens the block stages q, k (activation, unit norm, scale),
+// the decay of every key channel, v, beta and k.q in shared memory.  A column's update needs S^T k
+// before it can write, so that dot product closes with shuffles for every token; the read o = S^T q =
+// (g S)^T q + u (k.q) is linear in what a lane holds, so the lanes' shares are summed once per tile.
+
+constexpr int DR_WARPS = 16;
+constexpr int DR_TT = 32;
+
+struct DeltaParams {
+    const void* q; const void* k; const void* v;   // [N, ld*] views; q/k head j begins at column j * D, v head h at h * V
+    long long ldq, ldk, ldv;
+    const void* beta;          // [N, ldb] activation type: beta = sigmoid(beta[t, h])
+    long long ldb;
+    const float* g_raw;        // [N, H * D] float: decay pre-activations without their bias
+    const void* g_bias;        // [H * D]
+    const void* a_log;         // [H]: g = exp(-exp(a_log[h]) * softplus(g_raw + g_bias))
+    int p_dtype;               // element type of g_bias and a_log
+    float* state;              // [slots, H, D * V]
+    const int* slots; const int* cu_q;
+    float* out;                // [N, H * V] float
+    int H, HK, D, V, act, unit;
+    float q_scale, unit_eps;
+};
+
+__device__ __forceinline__ float dr_in(float z, int act) { return act ? d_silu(z) : z; }
+
+template <typename T, int DPT, int SL>
+__global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const DeltaParams p) {
+    constexpr int TT = DR_TT;
+    constexpr int THREADS = DR_WARPS * 32;
+    constexpr int DP = SL * DPT;
+    constexpr int WCOLS = 32 / SL;
+    constexpr int COLS = DR_WARPS * WCOLS;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                 // [TT][DP]
+    float* ks = qs + TT * DP;         // [TT][DP]
+    float* gs = ks + TT * DP;         // [TT][DP]
+    float* vs = gs + TT * DP;         // [TT][COLS]
+    float* bs = vs + TT * COLS;       // [TT] beta
+    float* kqs = bs + TT;             // [TT] k . q
+    const int D = p.D, V = p.V;
+    const int row = blockIdx.z, head = blockIdx.y;
+    const int kh = head / (p.H / p.HK);
+    const int q0 = p.cu_q[row], qlen = p.cu_q[row + 1] - q0;
+    if (qlen <= 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slice = lane & (SL - 1), colw = lane / SL;
+    const int lcol = warp * WCOLS + colw;
+    const int col = blockIdx.x * COLS + lcol;
+    const bool live = col < V;
+    float* st = p.state + ((size_t)p.slots[row] * p.H + head) * ((size_t)D * V);
+    float S[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
+        S[i] = (live && d < D) ? st[(size_t)d * V + col] : 0.f;
+    }
+    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)kh * D;
+    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)kh * D;
+    const T* vg = reinterpret_cast<const T*>(p.v) + (size_t)head * V;
+    const float neg_a = -expf(load_any(p.a_log, p.p_dtype, head));
+
+    for (int t0 = 0; t0 < qlen; t0 += TT) {
+        const int cnt = min(TT, qlen - t0);
+        __syncthreads();  // the tile before is consumed
+        for (int idx = threadIdx.x; idx < TT * DP; idx += THREADS) {
+            const int t = idx / DP, d = idx % DP;
+            float qv = 0.f, kv = 0.f, gv = 1.f;
+            if (t < cnt && d < D) {
+                const size_t tok = (size_t)(q0 + t0 + t);
+                qv = dr_in(to_f32<T>(qg[tok * p.ldq + d]), p.act);
+                kv = dr_in(to_f32<T>(kg[tok * p.ldk + d]), p.act);
+                const size_t ch = (size_t)head * D + d;
+                gv = expf(neg_a * d_softplus(p.g_raw[tok * ((size_t)p.H * D) + ch] + load_any(p.g_bias, p.p_dtype, ch)));
+            }
+            qs[idx] = qv;
+            ks[idx] = kv;
+            gs[idx] = gv;
+        }
+        for (int idx = threadIdx.x; idx < TT * COLS; idx += THREADS) {
+            const int t = idx / COLS, gc = blockIdx.x * COLS + idx % COLS;
+            vs[idx] = (t < cnt && gc < V) ? dr_in(to_f32<T>(vg[(size_t)(q0 + t0 + t) * p.ldv + gc]), p.act) : 0.f;
+        }
+        __syncthreads();
+        // unit vectors, the query's scale, k . q and beta: a warp per token
+        for (int t = warp; t < TT; t += DR_WARPS) {
+            float sq = 0.f, sk = 0.f;
+            for (int d = lane; d < DP; d += 32) {
+                sq = fmaf(qs[t * DP + d], qs[t * DP + d], sq);
+                sk = fmaf(ks[t * DP + d], ks[t * DP + d], sk);
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float rq = (p.unit ? rsqrtf(sq + p.unit_eps) : 1.f) * p.q_scale;
+            const float rk = p.unit ? rsqrtf(sk + p.unit_eps) : 1.f;
+            float kq = 0.f;
+            for (int d = lane; d < DP; d += 32) {
+                const float a = qs[t * DP + d] * rq, b = ks[t * DP + d] * rk;
+                qs[t * DP + d] = a;
+                ks[t * DP + d] = b;
+                kq = fmaf(a, b, kq);
+            }
+            kq = warp_sum(kq);
+            if (lane == 0) {
+                kqs[t] = kq;
+                bs[t] = t < cnt ? d_sigmoid(to_f32<T>(reinterpret_cast<const T*>(p.beta)[(size_t)(q0 + t0 + t) * p.ldb + head])) : 0.f;
+            }
+        }
+        __syncthreads();
+        float acc[TT];
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP) + slice;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP) + slice;
+            const float4* g4 = reinterpret_cast<const float4*>(gs + t * DP) + slice;
+            float dk0 = 0.f, dk1 = 0.f, dq0 = 0.f, dq1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 kk = k4[i * SL], qq = q4[i * SL], gg = g4[i * SL];
+                S[4 * i + 0] *= gg.x;
+                S[4 * i + 1] *= gg.y;
+                S[4 * i + 2] *= gg.z;
+                S[4 * i + 3] *= gg.w;
+                dk0 = fmaf(S[4 * i + 0], kk.x, dk0);
+                dk1 = fmaf(S[4 * i + 1], kk.y, dk1);
+                dk0 = fmaf(S[4 * i + 2], kk.z, dk0);
+                dk1 = fmaf(S[4 * i + 3], kk.w, dk1);
+                dq0 = fmaf(S[4 * i + 0], qq.x, dq0);
+                dq1 = fmaf(S[4 * i + 1], qq.y, dq1);
+                dq0 = fmaf(S[4 * i + 2], qq.z, dq0);
+                dq1 = fmaf(S[4 * i + 3], qq.w, dq1);
+            }
+            float dk = dk0 + dk1;
+#pragma unroll
+            for (int off = SL / 2; off >= 1; off >>= 1) dk += __shfl_xor_sync(0xffffffffu, dk, off);
+            const float u = bs[t] * (vs[t * COLS + lcol] - dk);
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 kk = k4[i * SL];
+                S[4 * i + 0] = fmaf(kk.x, u, S[4 * i + 0]);
+                S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
+                S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);
+                S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);
+            }
+            acc[t] = (dq0 + dq1) + (slice == 0 ? u * kqs[t] : 0.f);
+        }
+        // the lanes' shares of the reads, summed once per tile (a lane hands one half of what it holds to
+        // its partner and adds the partner's other half)
+#pragma unroll
+        for (int off = SL / 2, n = TT; off >= 1; off >>= 1, n >>= 1) {
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int j = 0; j < n / 2; ++j) {
+                const float send = upper ? acc[j] : acc[j + n / 2];
+                const float keep = upper ? acc[j + n / 2] : acc[j];
+                acc[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+        }
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < TT / SL; ++j) {
+                const int t = slice * (TT / SL) + j;
+                if (t < cnt) p.out[(size_t)(q0 + t0 + t) * ((size_t)p.H * V) + (size_t)head * V + col] = acc[j];
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
+            if (d < D) st[(size_t)d * V + col] = S[i];
+        }
+    }
+}
+
+// A step in which every request brings one token: a thread owns a column of S and walks its rows twice
+// (S^T k of the decayed state, then the write and the read), so that the lanes of a warp touch
+// consecutive floats of every row.
+template <typename T>
+__global__ void __launch_bounds__(128) delta_step_kernel(const DeltaParams p) {
+    __shared__ float qs[256], ks[256], gs[256], red[33];
+    const int D = p.D, V = p.V;
+    const int tok = blockIdx.z, head = blockIdx.y;   // (row r brings token r)
+    const int kh = head / (p.H / p.HK);
+    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)tok * p.ldq + (size_t)kh * D;
+    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)tok * p.ldk + (size_t)kh * D;
+    const float neg_a = -expf(load_any(p.a_log, p.p_dtype, head));
+    float sq = 0.f, sk = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float a = dr_in(to_f32<T>(qg[d]), p.act), b = dr_in(to_f32<T>(kg[d]), p.act);
+        qs[d] = a;
+        ks[d] = b;
+        sq = fmaf(a, a, sq);
+        sk = fmaf(b, b, sk);
+        const size_t ch = (size_t)head * D + d;
+        gs[d] = expf(neg_a * d_softplus(p.g_raw[(size_t)tok * ((size_t)p.H * D) + ch] + load_any(p.g_bias, p.p_dtype, ch)));
+    }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    const float rq = (p.unit ? rsqrtf(sq + p.unit_eps) : 1.f) * p.q_scale;
+    const float rk = p.unit ? rsqrtf(sk + p.unit_eps) : 1.f;
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= V) return;
+    const float beta = d_sigmoid(to_f32<T>(reinterpret_cast<const T*>(p.beta)[(size_t)tok * p.ldb + head]));
+    const float vj = dr_in(to_f32<T>(reinterpret_cast<const T*>(p.v)[(size_t)tok * p.ldv + (size_t)head * V + col]), p.act);
+    float* sp = p.state + ((size_t)p.slots[tok] * p.H + head) * ((size_t)D * V) + col;
+    float dk0 = 0.f, dk1 = 0.f;
+    int d = 0;
+    for (; d + 1 < D; d += 2) {
+        dk0 = fmaf(gs[d] * sp[(size_t)d * V], ks[d] * rk, dk0);
+        dk1 = fmaf(gs[d + 1] * sp[(size_t)(d + 1) * V], ks[d + 1] * rk, dk1);
+    }
+    if (d < D) dk0 = fmaf(gs[d] * sp[(size_t)d * V], ks[d] * rk, dk0);
+    const float u = beta * (vj - (dk0 + dk1));
+    float o0 = 0.f, o1 = 0.f;
+    for (d = 0; d + 1 < D; d += 2) {
+        const float s0 = fmaf(ks[d] * rk, u, gs[d] * sp[(size_t)d * V]);
+        const float s1 = fmaf(ks[d + 1] * rk, u, gs[d + 1] * sp[(size_t)(d + 1) * V]);
+        sp[(size_t)d * V] = s0;
+        sp[(size_t)(d + 1) * V] = s1;
+        o0 = fmaf(s0, qs[d] * rq, o0);
+        o1 = fmaf(s1, qs[d + 1] * rq, o1);
+    }
+    if (d < D) {
+        const float s0 = fmaf(ks[d] * rk, u, gs[d] * sp[(size_t)d * V]);
+        sp[(size_t)d * V] = s0;
+        o0 = fmaf(s0, qs[d] * rq, o0);
+    }
+    p.out[(size_t)tok * ((size_t)p.H * V) + (size_t)head * V + col] = o0 + o1;
+}
+
+template <typename T, int DPT, int SL>
+static int launch_delta_as(const DeltaParams& p, int rows, cudaStream_t stream) {
+    constexpr int COLS = DR_WARPS * (32 / SL);
+    const dim3 grid((p.V + COLS - 1) / COLS, p.H, rows);
+    const size_t smem = sizeof(float) * ((size_t)DR_TT * (3 * SL * DPT + COLS) + 2 * DR_TT);
+    auto kernel = delta_recurrence_kernel<T, DPT, SL>;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return EMS_ERR_LAUNCH;
+    kernel<<<grid, DR_WARPS * 32, smem, stream>>>(p);
+    return launch_status();
+}
+
+template <typename T>
+static int launch_delta(const DeltaParams& p, int rows, int N, cudaStream_t stream) {
+    if (N == rows) {
+        delta_step_kernel<T><<<dim3((p.V + 127) / 128, p.H, rows), 128, 0, stream>>>(p);
+        return launch_status();
+    }
+    if (p.D <= 32) return launch_delta_as<T, 4, 8>(p, rows, stream);
+    if (p.D <= 64) return launch_delta_as<T, 4, 16>(p, rows, stream);
+    if (p.D <= 128) return launch_delta_as<T, 4, 32>(p, rows, stream);
+    return launch_delta_as<T, 8, 32>(p, rows, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// dt = softplus(x[t, h] + bias[h]);  a[t, h] = exp(-exp(a_log[h]) dt);  b[t, h] = dt
+
+template <typename T>
+__global__ void ssm_gates_kernel(const T* __restrict__ x, long long ldx, const void* __restrict__ bias,
+                                 const void* __restrict__ a_log, int p_dtype, float* __restrict__ a,
+                                 float* __restrict__ b, int N, int H) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N * H) return;
+    const int t = i / H, h = i % H;
+    const float dt = d_softplus(to_f32<T>(x[(size_t)t * ldx + h]) + load_any(bias, p_dtype, h));
+    a[i] = expf(-expf(load_any(a_log, p_dtype, h)) * dt);
+    b[i] = dt;
+}
+
+// y = (o + skip[h] act(x)) * silu(z);  out = y / rms_group(y) * w.  One warp per (token, group), or a
+// block when a group is long.  o: float [N, C]; x, z: column ranges of wider buffers; head h owns the
+// columns [h * hv, (h + 1) * hv).
+template <typename T, bool BLOCK>
+__global__ void gate_group_norm_kernel(const float* __restrict__ o, const T* __restrict__ x, long long ldx, int x_act,
+                                       const void* __restrict__ skip, const T* __restrict__ z, long long ldz,
+                                       const void* __restrict__ w, int w_dtype, T* __restrict__ out, int N, int C,
+                                       int groups, int hv, float eps) {
+    __shared__ float red[33];
+    const int gs = C / groups;
+    int unit, lane, width;
+    if (BLOCK) { unit = blockIdx.x; lane = threadIdx.x; width = blockDim.x; }
+    else { unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); lane = threadIdx.x & 31; width = 32; }
+    if (unit >= N * groups) return;
+    const int tok = unit / groups, g = unit % groups;
+    auto value = [&](int ch) {
+        float y = o[(size_t)tok * C + ch];
+        if (skip) {
+            const float xv = to_f32<T>(x[(size_t)tok * ldx + ch]);
+            y = fmaf(load_any(skip, w_dtype, ch / hv), x_act ? d_silu(xv) : xv, y);
+        }
+        if (z) y *= d_silu(to_f32<T>(z[(size_t)tok * ldz + ch]));
+        return y;
+    };
+    float ss = 0.f;
+    for (int c = lane; c < gs; c += width) {
+        const float y = value(g * gs + c);
+        ss = fmaf(y, y, ss);
+    }
+    ss = BLOCK ? block_sum(ss, red) : warp_sum(ss);
+    const float r = rsqrtf(ss / gs + eps);
+    for (int c = lane; c < gs; c += width) {
+        const int ch = g * gs + c;
+        out[(size_t)tok * C + ch] = from_f32<T>(value(ch) * r * load_any(w, w_dtype, ch));
+    }
+}
+
+}  // namespace ems
+
+using namespace ems;
+
+EMS_EXPORT int ems_add_scaled_norm2(const void* d0, const void* d1, const void* d2, float s0, float s1, float s2,
+                                    float* residual, const void* g1, const void* g2, int g_dtype, float gain_offset,
+                                    float eps, void* out1, void* out2, int dtype, int n, int C, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    if (C <= 0 || (out1 && !g1) || (out2 && !g2)) return EMS_ERR_SHAPE;
+    int th = 32;
+    while (th < 256 && th * 4 < C) th <<= 1;
+    if (dtype == EMS_F32)
+        add_scaled_norm2_kernel<float><<<n, th, 0, stream>>>((const float*)d0, (const float*)d1, (const float*)d2, s0, s1,
+                                                             s2, residual, g1, g2, g_dtype, gain_offset, eps,
+                                                             (float*)out1, (float*)out2, C);
+    else if (dtype == EMS_BF16)
+        add_scaled_norm2_kernel<bf16><<<n, th, 0, stream>>>((const bf16*)d0, (const bf16*)d1, (const bf16*)d2, s0, s1, s2,
+                                                            residual, g1, g2, g_dtype, gain_offset, eps, (bf16*)out1,
+                                                            (bf16*)out2, C);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_stream_norm(float* residual, const void* gain, int g_dtype, float gain_offset, float eps, int n,
+                               int C, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    if (C <= 0) return EMS_ERR_SHAPE;
+    int th = 32;
+    while (th < 256 && th * 4 < C) th <<= 1;
+    stream_norm_kernel<<<n, th, 0, stream>>>(residual, gain, g_dtype, gain_offset, eps, C);
+    return launch_status();
+}
+
+EMS_EXPORT int ems_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return EMS_OK;
+    if (!(cap > 0.f)) return EMS_ERR_SHAPE;
+    const long long blocks = (n + 255) / 256;
+    softcap_kernel<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, stream>>>(x, (size_t)n, cap);
+    return launch_status();
+}
+
+EMS_EXPORT int ems_delta_recurrence(const void* q, long long ldq, const void* k, long long ldk, const void* v,
+                                    long long ldv, const void* beta, long long ldb, int dtype, int act, int unit,
+                                    float unit_eps, float q_scale, const float* g_raw, const void* g_bias,
+                                    const void* a_log, int p_dtype, float* state, const int* slots, const int* cu_q,
+                                    int rows, int N, int H, int HK, int D, int V, float* out, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return EMS_OK;
+    if (H <= 0 || HK <= 0 || H % HK || D <= 0 || D > 256 || V <= 0 || H > 65535 || rows > 65535) return EMS_ERR_SHAPE;
+    DeltaParams p;
+    p.q = q; p.k = k; p.v = v; p.ldq = ldq; p.ldk = ldk; p.ldv = ldv; p.beta = beta; p.ldb = ldb; p.g_raw = g_raw;
+    p.g_bias = g_bias; p.a_log = a_log; p.p_dtype = p_dtype; p.state = state; p.slots = slots; p.cu_q = cu_q;
+    p.out = out; p.H = H; p.HK = HK; p.D = D; p.V = V; p.act = act; p.unit = unit; p.q_scale = q_scale;
+    p.unit_eps = unit_eps;
+    if (dtype == EMS_F32) return launch_delta<float>(p, rows, N, stream);
+    if (dtype == EMS_BF16) return launch_delta<bf16>(p, rows, N, stream);
+    return EMS_ERR_DTYPE;
+}
+
+EMS_EXPORT int ems_ssm_gates(const void* x, long long ldx, int dtype, const void* bias, const void* a_log, int p_dtype,
+                             float* a, float* b, int N, int H, cudaStream_t stream) {
+    if (N <= 0) return EMS_OK;
+    if (H <= 0) return EMS_ERR_SHAPE;
+    const unsigned blocks = (unsigned)(((long long)N * H + 255) / 256);
+    if (dtype == EMS_F32)
+        ssm_gates_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, ldx, bias, a_log, p_dtype, a, b, N, H);
+    else if (dtype == EMS_BF16)
+        ssm_gates_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, bias, a_log, p_dtype, a, b, N, H);
+    else
+        return EMS_ERR_DTYPE;
+    return launch_status();
+}
+
+EMS_EXPORT int ems_gate_group_norm(const float* o, const void* x, long long ldx, int x_act, const void* skip,
+                                   const void* z, long long ldz, const void* w, int w_dtype, void* out, int dtype,
+                                   int N, int C, int groups, int hv, float eps, cudaStream_t stream) {
+    if (N <= 0) return EMS_OK;
+    if (groups <= 0 || C % groups || hv <= 0 || C % hv || (skip && !x)) return EMS_ERR_SHAPE;
+    const int gs = C / groups;
+    const long long units = (long long)N * groups;
+#define EMS_LAUNCH_GGN(T)                                                                                          \
+    do {                                                                                                           \
+        if (gs > 256)                                                                                              \
+            gate_group_norm_kernel<T, true><<<(unsigned)units, gs > 1024 ? 256 : 128, 0, stream>>>(                \
+                o, (const T*)x, ldx, x_act, skip, (const T*)z, ldz, w, w_dtype, (T*)out, N, C, groups, hv, eps);   \
+        else                                                                                                       \
+            gate_group_norm_kernel<T, false><<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(                     \
+                o, (const T*)x, ldx, x_act, skip, (const T*)z, ldz, w, w_dtype, (T*)out, N, C, groups, hv, eps);   \
+    } while (0)
+    if (dtype == EMS_F32) EMS_LAUNCH_GGN(float);
+    else if (dtype == EMS_BF16) EMS_LAUNCH_GGN(bf16);
+    else return EMS_ERR_DTYPE;
+#undef EMS_LAUNCH_GGN
+    return launch_status();
+}

@@ -16,11 +16,13 @@ namespace ems {
 #define EMS_ACT_RELU2 1
 #define EMS_ACT_GELU_TANH 2
 #define EMS_ACT_SILU 3
+#define EMS_ACT_GELU_ERF 4
 
 __device__ __forceinline__ float unary_activation(float z, int act) {
     if (act == EMS_ACT_RELU) return fmaxf(z, 0.f);
     if (act == EMS_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
     if (act == EMS_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (act == EMS_ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
     return z / (1.f + expf(-z));
 }
 
@@ -54,7 +56,8 @@ __global__ void qk_prep_kernel(T* __restrict__ proj, long long ld, int nh, int n
                                const float* __restrict__ table, int rot, int pairing, int normed, float eps,
                                T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ bt, int bt_stride,
                                int page_size, int values_are_keys, int write_kv, int DV, int v_normed, float v_eps,
-                               const float* __restrict__ v_table, int v_pairing) {
+                               const float* __restrict__ v_table, int v_pairing, const void* __restrict__ q_gain,
+                               const void* __restrict__ k_gain, int gain_dtype, int norm_first) {
     extern __shared__ float smem[];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -109,6 +112,14 @@ __global__ void qk_prep_kernel(T* __restrict__ proj, long long ld, int nh, int n
             if (vdst) vdst[d] = raw;
         }
         __syncwarp();
+        const void* gain = is_k ? k_gain : q_gain;   // [D], shared by the heads (optional)
+        if (normed && norm_first) {   // the norm (with its gain) comes before the rotation
+            float ss = 0.f;
+            for (int d = lane; d < D; d += 32) ss = fmaf(buf[d], buf[d], ss);
+            const float r0 = rsqrtf(warp_sum(ss) / D + eps);
+            for (int d = lane; d < D; d += 32) buf[d] = buf[d] * r0 * (gain ? load_any(gain, gain_dtype, d) : 1.f);
+            __syncwarp();
+        }
         if (cs) {
             for (int i = lane; i < half; i += 32) {
                 const int ia = pairing ? 2 * i : i, ib = pairing ? 2 * i + 1 : i + half;
@@ -120,10 +131,14 @@ __global__ void qk_prep_kernel(T* __restrict__ proj, long long ld, int nh, int n
             __syncwarp();
         }
         float r = 1.f;
-        if (normed) {
+        if (normed && !norm_first) {
             float ss = 0.f;
             for (int d = lane; d < D; d += 32) ss = fmaf(buf[d], buf[d], ss);
             r = rsqrtf(warp_sum(ss) / D + eps);
+            if (gain) {
+                for (int d = lane; d < D; d += 32) buf[d] *= load_any(gain, gain_dtype, d);
+                __syncwarp();
+            }
         }
         for (int d = lane; d < D; d += 32) {
             const T val = from_f32<T>(buf[d] * r);
@@ -161,7 +176,7 @@ using namespace ems;
 
 EMS_EXPORT int ems_unary_act(const void* x, void* out, int dtype, long long n, int act, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
-    if (act < 0 || act > 3) return EMS_ERR_SHAPE;
+    if (act < 0 || act > 4) return EMS_ERR_SHAPE;
     const int per = dtype == EMS_F32 ? 4 : 8;
     if ((dtype == EMS_F32 || dtype == EMS_BF16) && n % per == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0) {
         const size_t nvec = (size_t)(n / per);
@@ -183,6 +198,7 @@ EMS_EXPORT int ems_qk_prep(void* proj, long long ld, int dtype, int n, int nh, i
                            const int* row_of_token, const float* table, int rot, int pairing, int normed, float eps,
                            void* kc, void* vc, const int* bt, int bt_stride, int page_size, int values_are_keys,
                            int write_kv, int DV, int v_normed, float v_eps, const float* v_table, int v_pairing,
+                           const void* q_gain, const void* k_gain, int gain_dtype, int norm_first,
                            cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     if (DV <= 0) DV = D;
@@ -199,12 +215,14 @@ EMS_EXPORT int ems_qk_prep(void* proj, long long ld, int dtype, int n, int nh, i
         qk_prep_kernel<float><<<n, warps * 32, smem, stream>>>((float*)proj, ld, nh, nkv, D, positions, row_of_token, tab,
                                                                rot, pairing, normed, eps, (float*)kc, (float*)vc, bt,
                                                                bt_stride, page_size, values_are_keys, write_kv, DV,
-                                                               v_normed, v_eps, v_table, v_pairing);
+                                                               v_normed, v_eps, v_table, v_pairing, q_gain, k_gain,
+                                                               gain_dtype, norm_first);
     else if (dtype == EMS_BF16)
         qk_prep_kernel<bf16><<<n, warps * 32, smem, stream>>>((bf16*)proj, ld, nh, nkv, D, positions, row_of_token, tab,
                                                               rot, pairing, normed, eps, (bf16*)kc, (bf16*)vc, bt,
                                                               bt_stride, page_size, values_are_keys, write_kv, DV,
-                                                              v_normed, v_eps, v_table, v_pairing);
+                                                              v_normed, v_eps, v_table, v_pairing, q_gain, k_gain,
+                                                              gain_dtype, norm_first);
     else
         return EMS_ERR_DTYPE;
     return launch_status();

@@ -6,7 +6,10 @@
 //             s = softmax(z) over all experts; the `top` largest (ties: the lower index) are
 //             chosen; their weights are the scores s as they are (renorm = 0) or divided by
 //             their sum (renorm = 1).  With scoring = 1 the scores are sigmoid(z) instead, each
-//             expert by itself.  The same kernel counts the pairs per expert, lays the
+//             expert by itself.  With a correction vector c the choice is made by s + c while the
+//             weights stay the scores s; the weights may be divided by (their sum + an epsilon) and
+//             multiplied by a constant; experts at and past `plan_experts` get no tiles (they have
+//             no weights: the combine step returns their input).  The same kernel counts the pairs per expert, lays the
 //             pairs out expert by expert (perm) and cuts each expert's rows into tiles.
 //   up        act[i, :] = f(x[token(i)] Wg[e]^T) * (x[token(i)] Wu[e]^T)   for sorted pair i of expert e
 //   down      y[pair(i), :] = act[i, :] Wd[e]^T            (32-bit, in pair order)
@@ -23,9 +26,16 @@ constexpr int MOE_TM = 64, MOE_TN = 64, MOE_TK = 16;
 
 // One warp chooses for one token: lane l holds the logits of experts l, l + 32, ... (up to 8 each,
 // so up to 256 experts; more are chosen by one lane alone).  Ties go to the lower index.
-__device__ __forceinline__ void moe_choose_serial(const float* __restrict__ z, int E, int top, int renorm,
-                                                  int* __restrict__ ids, float* __restrict__ wts, int* counts,
-                                                  int scoring) {
+struct MoeRoute {
+    int top, renorm, scoring;
+    const float* corr;   // [E] added to the scores for the choice only, or null
+    float renorm_eps;    // joins the sum the chosen scores are divided by
+    float scale;         // multiplies the weights
+};
+
+__device__ __forceinline__ void moe_choose_serial(const float* __restrict__ z, int E, const MoeRoute r,
+                                                  int* __restrict__ ids, float* __restrict__ wts, int* counts) {
+    const int top = r.top;
     float mx = -INFINITY;
     for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[e]);
     float sum = 0.f;
@@ -33,34 +43,36 @@ __device__ __forceinline__ void moe_choose_serial(const float* __restrict__ z, i
     float chosen_sum = 0.f;
     for (int k = 0; k < top; ++k) {
         int best = -1;
-        float bv = -INFINITY;
+        float bv = -INFINITY, bs = 0.f;
         for (int e = 0; e < E; ++e) {
             bool taken = false;
             for (int j = 0; j < k; ++j) taken |= ids[j] == e;
-            if (!taken && (best < 0 || z[e] > bv)) {
+            if (taken) continue;
+            const float sc = r.scoring ? 1.f / (1.f + expf(-z[e])) : expf(z[e] - mx) / sum;
+            const float cv = r.corr ? sc + r.corr[e] : z[e];   // (without a correction the logits order the scores)
+            if (best < 0 || cv > bv) {
                 best = e;
-                bv = z[e];
+                bv = cv;
+                bs = sc;
             }
         }
         ids[k] = best;
-        const float s = scoring ? 1.f / (1.f + expf(-bv)) : expf(bv - mx) / sum;
-        wts[k] = s;
-        chosen_sum += s;
+        wts[k] = bs;
+        chosen_sum += bs;
         atomicAdd(&counts[best], 1);
     }
-    if (renorm)
-        for (int k = 0; k < top; ++k) wts[k] /= chosen_sum;
+    for (int k = 0; k < top; ++k) wts[k] = (r.renorm ? wts[k] / (chosen_sum + r.renorm_eps) : wts[k]) * r.scale;
 }
 
-__device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int E, int top, int renorm,
-                                                int* __restrict__ ids, float* __restrict__ wts, int* counts,
-                                                int scoring) {
+__device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int E, const MoeRoute r,
+                                                int* __restrict__ ids, float* __restrict__ wts, int* counts) {
     const int lane = threadIdx.x & 31;
+    const int top = r.top;
     if (E > 256) {
-        if (lane == 0) moe_choose_serial(z, E, top, renorm, ids, wts, counts, scoring);
+        if (lane == 0) moe_choose_serial(z, E, r, ids, wts, counts);
         return;
     }
-    float v[8];
+    float v[8], sc[8];   // what orders the choice, and the score
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -74,31 +86,39 @@ __device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int
     for (int i = 0; i < 8; ++i)
         if (lane + 32 * i < E) sum += expf(v[i] - mx);
     sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        sc[i] = e < E ? (r.scoring ? 1.f / (1.f + expf(-v[i])) : expf(v[i] - mx) / sum) : 0.f;
+        if (r.corr && e < E) v[i] = sc[i] + r.corr[e];   // (without a correction the logits order the scores)
+    }
     float chosen_sum = 0.f;
     unsigned taken = 0u;  // bit i: my expert lane + 32 i is chosen already
     for (int k = 0; k < top; ++k) {
-        float bv = -INFINITY;
+        float bv = -INFINITY, bs = 0.f;
         int bi = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < 8; ++i)
             if (lane + 32 * i < E && !((taken >> i) & 1u) && (bi == 0x7fffffff || v[i] > bv)) {
                 bv = v[i];
+                bs = sc[i];
                 bi = lane + 32 * i;
             }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const float os = __shfl_xor_sync(0xffffffffu, bs, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
                 bv = ov;
+                bs = os;
                 bi = oi;
             }
         }
-        const float s = scoring ? 1.f / (1.f + expf(-bv)) : expf(bv - mx) / sum;
-        chosen_sum += s;
+        chosen_sum += bs;
         if (lane == 0) {
             ids[k] = bi;
-            wts[k] = s;
+            wts[k] = bs;
             atomicAdd(&counts[bi], 1);
         }
 #pragma unroll
@@ -106,15 +126,16 @@ __device__ __forceinline__ void moe_choose_warp(const float* __restrict__ z, int
             if (lane + 32 * i == bi) taken |= 1u << i;
     }
     __syncwarp();
-    if (renorm && lane == 0)
-        for (int k = 0; k < top; ++k) wts[k] /= chosen_sum;
+    if (lane == 0)
+        for (int k = 0; k < top; ++k) wts[k] = (r.renorm ? wts[k] / (chosen_sum + r.renorm_eps) : wts[k]) * r.scale;
 }
 
 // plan (int32): [0] number of tiles; [1 .. 1 + 3 * max_tiles) expert, first sorted row and row
 // count of each tile.  One block.
-__global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
+__global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E, const MoeRoute r,
                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ offsets,
-                                 int* __restrict__ perm, int* __restrict__ plan, int max_tiles, int scoring) {
+                                 int* __restrict__ perm, int* __restrict__ plan, int max_tiles, int plan_experts) {
+    const int top = r.top;
     extern __shared__ int sh[];
     int* counts = sh;       // [E]
     int* cursor = sh + E;   // [E]
@@ -122,8 +143,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E,
     for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
     __syncthreads();
     for (int t = threadIdx.x >> 5; t < n; t += blockDim.x >> 5)
-        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts,
-                        scoring);
+        moe_choose_warp(logits + (size_t)t * E, E, r, ids + (size_t)t * top, wts + (size_t)t * top, counts);
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0, nt = 0;
@@ -131,7 +151,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E,
             offs[e] = run;
             offsets[e] = run;
             cursor[e] = 0;
-            for (int r0 = 0; r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
+            for (int r0 = 0; e < plan_experts && r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
                 plan[1 + 3 * nt] = e;
                 plan[2 + 3 * nt] = run + r0;
                 plan[3 + 3 * nt] = min(MOE_TM, counts[e] - r0);
@@ -153,13 +173,11 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n, int E,
 // The same in three kernels for steps of many tokens: one warp per token chooses and counts
 // (counts in global memory, zeroed before), one block lays out offsets and tiles, one thread per
 // pair takes its place among its expert's rows.
-__global__ void moe_choose_kernel(const float* __restrict__ logits, int n, int E, int top, int renorm,
-                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
-                                  int scoring) {
+__global__ void moe_choose_kernel(const float* __restrict__ logits, int n, int E, const MoeRoute r,
+                                  int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts) {
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t < n)
-        moe_choose_warp(logits + (size_t)t * E, E, top, renorm, ids + (size_t)t * top, wts + (size_t)t * top, counts,
-                        scoring);
+        moe_choose_warp(logits + (size_t)t * E, E, r, ids + (size_t)t * r.top, wts + (size_t)t * r.top, counts);
 }
 
 // offsets: [E + 1]; counts and cursor: [E] each (the cursors are set to zero here).  With align > 1
@@ -167,7 +185,7 @@ __global__ void moe_choose_kernel(const float* __restrict__ logits, int n, int E
 // names the expert of the m-th group of `align` rows, -1 where the group is not in use.
 __global__ void moe_plan_kernel(int E, const int* __restrict__ counts, int* __restrict__ cursor,
                                 int* __restrict__ offsets, int* __restrict__ plan, int max_tiles, int align,
-                                int* __restrict__ big, int max_big) {
+                                int* __restrict__ big, int max_big, int plan_experts) {
     if (threadIdx.x != 0) return;
     int run = 0, nt = 0, nb = 0;
     for (int e = 0; e < E; ++e) {
@@ -175,8 +193,8 @@ __global__ void moe_plan_kernel(int E, const int* __restrict__ counts, int* __re
         offsets[e] = run;
         cursor[e] = 0;
         if (big)
-            for (int r0 = 0; r0 < counts[e] && nb < max_big; r0 += align) big[nb++] = e;
-        for (int r0 = 0; r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
+            for (int r0 = 0; r0 < counts[e] && nb < max_big; r0 += align) big[nb++] = e < plan_experts ? e : -1;
+        for (int r0 = 0; e < plan_experts && r0 < counts[e] && nt < max_tiles; r0 += MOE_TM, ++nt) {
             plan[1 + 3 * nt] = e;
             plan[2 + 3 * nt] = run + r0;
             plan[3 + 3 * nt] = min(MOE_TM, counts[e] - r0);
@@ -215,6 +233,7 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, int pairs, const
 __device__ __forceinline__ float moe_activation(float g, int act) {
     if (act == 1) return fmaxf(g, 0.f);
     if (act == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    if (act == 4) return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));
     return g / (1.f + expf(-g));
 }
 
@@ -237,17 +256,20 @@ __device__ __forceinline__ float moe_glu(float cg, float cu, float s, const MoeA
     return moe_activation(g, a.act) * u;
 }
 
-// GLU = true:  A rows are x[perm[row] / top] (gathered), B = w[e] of shape [2 N, K]; the tile
+// MODE 1 (gated up): A rows are x[perm[row] / top] (gathered), B = w[e] of shape [2 N, K]; the tile
 //              computes gate and up columns side by side and stores f(gate) * up in sorted order.
-// GLU = false: A rows are a[row] (sorted order), B = w[e] of shape [N, K]; the tile is stored at
+// MODE 2 (plain up): A rows gathered likewise, B = w[e] of shape [N, K]; the tile stores f(sum) in
+//              sorted order (an expert without a gate).
+// MODE 0 (down): A rows are a[row] (sorted order), B = w[e] of shape [N, K]; the tile is stored at
 //              rows perm[row] of a 32-bit output.
-template <typename T, bool GLU>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* __restrict__ perm,
                    const int* __restrict__ plan, int top, int N, int K, const MoeAct act, T* __restrict__ out_t,
                    float* __restrict__ out_f, const float* __restrict__ in_scale) {
     __shared__ float As[MOE_TK][MOE_TM + 4];
     __shared__ float Bs[MOE_TK][MOE_TN + 4];
+    constexpr bool GLU = MODE == 1;
     __shared__ float Bu[GLU ? MOE_TK : 1][MOE_TN + 4];
     __shared__ int src_row[MOE_TM];
     const int tile = blockIdx.x;
@@ -256,7 +278,7 @@ moe_grouped_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* 
     const int n0 = blockIdx.y * MOE_TN;
     const T* we = w + (size_t)e * (GLU ? 2 : 1) * N * K;
     for (int i = threadIdx.x; i < MOE_TM; i += blockDim.x)
-        src_row[i] = i < rows ? (GLU ? perm[row0 + i] / top : row0 + i) : -1;
+        src_row[i] = i < rows ? (MODE != 0 ? perm[row0 + i] / top : row0 + i) : -1;
     __syncthreads();
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     const int lr = threadIdx.x / 4, lk = (threadIdx.x % 4) * 4;  // the loader's row and first column
@@ -308,6 +330,9 @@ moe_grouped_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* 
             if (GLU) {
                 const float sc = in_scale ? in_scale[perm[row0 + r]] : 1.f;
                 out_t[(size_t)(row0 + r) * N + c] = from_f32<T>(moe_glu<T>(cg[i][j], cu[i][j], sc, act));
+            } else if (MODE == 2) {
+                const float sc = in_scale ? in_scale[perm[row0 + r]] : 1.f;
+                out_t[(size_t)(row0 + r) * N + c] = from_f32<T>(moe_activation(round_to<T>(sc * cg[i][j]), act.act));
             } else {
                 out_f[(size_t)perm[row0 + r] * N + c] = round_to<T>(cg[i][j]);
             }
@@ -342,7 +367,7 @@ __device__ __forceinline__ void mm_mma(float (&c)[4], const uint32_t (&a)[4], ui
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool GLU>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, const int* __restrict__ perm,
                        const int* __restrict__ plan, int top, int N, int K, const MoeAct act, bf16* __restrict__ out_t,
@@ -352,6 +377,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, c
     bf16* As = reinterpret_cast<bf16*>(mm_smem);      // [MM_STAGES][MM_TM][LDS]
     bf16* Bs = As + MM_STAGES * MM_TM * LDS;          // [MM_STAGES][MM_TB][LDS]
     __shared__ int src_row[MM_TM];
+    constexpr bool GLU = MODE == 1;
     const int tile = blockIdx.x;
     if (tile >= plan[0]) return;
     const int e = plan[1 + 3 * tile], row0 = plan[2 + 3 * tile], rows = plan[3 + 3 * tile];
@@ -359,7 +385,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, c
     const int n0 = blockIdx.y * NOUT;
     const bf16* we = w + (size_t)e * (GLU ? 2 : 1) * N * K;
     for (int i = threadIdx.x; i < MM_TM; i += blockDim.x)
-        src_row[i] = i < rows ? (GLU ? perm[row0 + i] / top : row0 + i) : -1;
+        src_row[i] = i < rows ? (MODE != 0 ? perm[row0 + i] / top : row0 + i) : -1;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps: 32 rows x (GLU ? 16 + 16 : 32) weight rows each
@@ -450,6 +476,17 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, c
                         out_t[(size_t)(row0 + r) * N + c] = from_f32<bf16>(
                             moe_glu<bf16>(acc[i][nt][2 * hrow + x], acc[i][2 + nt][2 * hrow + x], sc, act));
                     }
+            } else if (MODE == 2) {
+                const float sc = in_scale ? in_scale[perm[row0 + r]] : 1.f;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const int c = n0 + wn * 32 + nt * 8 + 2 * tq + x;
+                        if (c < N)
+                            out_t[(size_t)(row0 + r) * N + c] = from_f32<bf16>(
+                                moe_activation(round_to<bf16>(sc * acc[i][nt][2 * hrow + x]), act.act));
+                    }
             } else {
                 float* dst = out_f + (size_t)perm[row0 + r] * N;
 #pragma unroll
@@ -469,13 +506,18 @@ static bool moe_mma_ok(const void* a, const void* w, int K) {
 
 // wts may be null (every weight 1: the scores went into the experts' inputs); `extra` (optional, [n, H]) is
 // added last: the output of an expert that every token uses.
+// With `ids` and `x`, a choice whose expert is at or past `num_real` has no weights: its output is the token's input x[t].
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wts, T* __restrict__ out,
-                                   int top, int H, const T* __restrict__ extra) {
+                                   int top, int H, const T* __restrict__ extra, const int* __restrict__ ids,
+                                   const T* __restrict__ x, int num_real) {
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s = fmaf(wts ? wts[t * top + k] : 1.f, y[(t * top + k) * H + c], s);
+        for (int k = 0; k < top; ++k) {
+            const bool same = ids && ids[t * top + k] >= num_real;
+            s = fmaf(wts ? wts[t * top + k] : 1.f, same ? to_f32<T>(x[t * H + c]) : y[(t * top + k) * H + c], s);
+        }
         if (extra) s += to_f32<T>(extra[t * H + c]);
         out[t * H + c] = from_f32<T>(s);
     }
@@ -517,29 +559,31 @@ EMS_EXPORT int ems_moe_tile_rows() { return MOE_TM; }
 // sorted row of every pair.
 EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int renorm, int* ids, float* wts,
                              int* offsets, int* perm, int* plan, int max_tiles, int align, int* big, int max_big,
-                             int* inv, int scoring, cudaStream_t stream) {
+                             int* inv, int scoring, const float* corr, float renorm_eps, float scale,
+                             int plan_experts, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     if (top < 1 || top > E || scoring < 0 || scoring > 1) return EMS_ERR_SHAPE;
     if (align < 1 || (align > 1 && (n <= 512 || !big || max_big < n * top / align + (E < n * top ? E : n * top))))
         return EMS_ERR_SHAPE;
+    if (plan_experts <= 0 || plan_experts > E) plan_experts = E;   // (every expert has weights)
+    const MoeRoute r{top, renorm, scoring, corr, renorm_eps, scale};
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     if (smem > 48 * 1024) return EMS_ERR_SHAPE;
     if (n > 512) {  // `offsets` holds [offsets (E + 1) | counts (E) | cursors (E)]
         int* counts = offsets + E + 1;
         int* cursor = counts + E;
         if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), stream) != cudaSuccess) return EMS_ERR_LAUNCH;
-        moe_choose_kernel<<<(n + 7) / 8, 256, 0, stream>>>(logits, n, E, top, renorm, ids, wts, counts, scoring);
+        moe_choose_kernel<<<(n + 7) / 8, 256, 0, stream>>>(logits, n, E, r, ids, wts, counts);
         if (align > 1 &&
             cudaMemsetAsync(perm, 0xFF, (size_t)max_big * align * sizeof(int), stream) != cudaSuccess)
             return EMS_ERR_LAUNCH;
         moe_plan_kernel<<<1, 32, 0, stream>>>(E, counts, cursor, offsets, plan, max_tiles, align,
-                                              align > 1 ? big : nullptr, max_big);
+                                              align > 1 ? big : nullptr, max_big, plan_experts);
         moe_scatter_kernel<<<(n * top + 255) / 256, 256, 0, stream>>>(ids, n * top, offsets, cursor, perm, inv);
         return launch_status();
     }
     int th = 32 * (n < 32 ? n : 32);  // a warp per token, up to 32 warps
-    moe_route_kernel<<<1, th, smem, stream>>>(logits, n, E, top, renorm, ids, wts, offsets, perm, plan, max_tiles,
-                                              scoring);
+    moe_route_kernel<<<1, th, smem, stream>>>(logits, n, E, r, ids, wts, offsets, perm, plan, max_tiles, plan_experts);
     return launch_status();
 }
 
@@ -547,24 +591,43 @@ EMS_EXPORT int ems_moe_route(const float* logits, int n, int E, int top, int ren
 // in_scale (optional, [pairs] float): the factor on the input of each (token, choice) pair's expert.
 EMS_EXPORT int ems_moe_up(const void* x, const void* wgu, int dtype, const int* perm, const int* plan, int max_tiles,
                           int top, int ff, int K, int act_code, void* out, int impl, const float* in_scale,
-                          float limit, float alpha, cudaStream_t stream) {
+                          float limit, float alpha, int gated, cudaStream_t stream) {
     if (max_tiles <= 0) return EMS_OK;
-    if (act_code < 0 || act_code > 3) return EMS_ERR_SHAPE;
+    if (act_code < 0 || act_code > 4 || (gated == 0 && act_code == 3)) return EMS_ERR_SHAPE;
     const MoeAct act{act_code, limit, alpha};
+    if (!gated) {   // experts without a gate: wgu is [E, ff, K]
+        if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(x, wgu, K)) {
+            dim3 mg(max_tiles, (ff + MM_TB - 1) / MM_TB);
+            cudaFuncSetAttribute(moe_grouped_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
+            moe_grouped_mma_kernel<2><<<mg, 256, MM_SMEM, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top, ff,
+                                                                 K, act, (bf16*)out, nullptr, in_scale);
+            return launch_status();
+        }
+        dim3 grid(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
+        if (dtype == EMS_F32)
+            moe_grouped_kernel<float, 2><<<grid, 256, 0, stream>>>((const float*)x, (const float*)wgu, perm, plan, top,
+                                                                   ff, K, act, (float*)out, nullptr, in_scale);
+        else if (dtype == EMS_BF16)
+            moe_grouped_kernel<bf16, 2><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top,
+                                                                  ff, K, act, (bf16*)out, nullptr, in_scale);
+        else
+            return EMS_ERR_DTYPE;
+        return launch_status();
+    }
     // impl: 0 the tensor-core kernel where it takes the case, 1 always the CUDA-core kernel
     if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(x, wgu, K)) {
         dim3 mg(max_tiles, (ff + MM_TB / 2 - 1) / (MM_TB / 2));
-        cudaFuncSetAttribute(moe_grouped_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
-        moe_grouped_mma_kernel<true><<<mg, 256, MM_SMEM, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top, ff, K,
+        cudaFuncSetAttribute(moe_grouped_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
+        moe_grouped_mma_kernel<1><<<mg, 256, MM_SMEM, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top, ff, K,
                                                              act, (bf16*)out, nullptr, in_scale);
         return launch_status();
     }
     dim3 grid(max_tiles, (ff + MOE_TN - 1) / MOE_TN);
     if (dtype == EMS_F32)
-        moe_grouped_kernel<float, true><<<grid, 256, 0, stream>>>((const float*)x, (const float*)wgu, perm, plan, top,
+        moe_grouped_kernel<float, 1><<<grid, 256, 0, stream>>>((const float*)x, (const float*)wgu, perm, plan, top,
                                                                   ff, K, act, (float*)out, nullptr, in_scale);
     else if (dtype == EMS_BF16)
-        moe_grouped_kernel<bf16, true><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top,
+        moe_grouped_kernel<bf16, 1><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)wgu, perm, plan, top,
                                                                  ff, K, act, (bf16*)out, nullptr, in_scale);
     else
         return EMS_ERR_DTYPE;
@@ -576,17 +639,17 @@ EMS_EXPORT int ems_moe_down(const void* a, const void* wdown, int dtype, const i
     if (max_tiles <= 0) return EMS_OK;
     if (dtype == EMS_BF16 && impl == 0 && moe_mma_ok(a, wdown, ff)) {
         dim3 mg(max_tiles, (H + MM_TB - 1) / MM_TB);
-        cudaFuncSetAttribute(moe_grouped_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
-        moe_grouped_mma_kernel<false><<<mg, 256, MM_SMEM, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1, H, ff,
+        cudaFuncSetAttribute(moe_grouped_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, MM_SMEM);
+        moe_grouped_mma_kernel<0><<<mg, 256, MM_SMEM, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1, H, ff,
                                                               MoeAct{0, 0.f, 0.f}, nullptr, y, nullptr);
         return launch_status();
     }
     dim3 grid(max_tiles, (H + MOE_TN - 1) / MOE_TN);
     if (dtype == EMS_F32)
-        moe_grouped_kernel<float, false><<<grid, 256, 0, stream>>>((const float*)a, (const float*)wdown, perm, plan, 1,
+        moe_grouped_kernel<float, 0><<<grid, 256, 0, stream>>>((const float*)a, (const float*)wdown, perm, plan, 1,
                                                                    H, ff, MoeAct{0, 0.f, 0.f}, nullptr, y, nullptr);
     else if (dtype == EMS_BF16)
-        moe_grouped_kernel<bf16, false><<<grid, 256, 0, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1,
+        moe_grouped_kernel<bf16, 0><<<grid, 256, 0, stream>>>((const bf16*)a, (const bf16*)wdown, perm, plan, 1,
                                                                   H, ff, MoeAct{0, 0.f, 0.f}, nullptr, y, nullptr);
     else
         return EMS_ERR_DTYPE;
@@ -604,12 +667,12 @@ EMS_EXPORT int ems_moe_gather(const void* x, const int* perm, int rows, int top,
 }
 
 EMS_EXPORT int ems_moe_combine(const float* y, const float* wts, void* out, int dtype, int n, int top, int H,
-                               const void* extra, cudaStream_t stream) {
+                               const void* extra, const int* ids, const void* x, int num_real, cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     int th = 32;
     while (th < H && th < 256) th <<= 1;
-    if (dtype == EMS_F32) moe_combine_kernel<float><<<n, th, 0, stream>>>(y, wts, (float*)out, top, H, (const float*)extra);
-    else if (dtype == EMS_BF16) moe_combine_kernel<bf16><<<n, th, 0, stream>>>(y, wts, (bf16*)out, top, H, (const bf16*)extra);
+    if (dtype == EMS_F32) moe_combine_kernel<float><<<n, th, 0, stream>>>(y, wts, (float*)out, top, H, (const float*)extra, x ? ids : nullptr, (const float*)x, num_real);
+    else if (dtype == EMS_BF16) moe_combine_kernel<bf16><<<n, th, 0, stream>>>(y, wts, (bf16*)out, top, H, (const bf16*)extra, x ? ids : nullptr, (const bf16*)x, num_real);
     else return EMS_ERR_DTYPE;
     return launch_status();
 }

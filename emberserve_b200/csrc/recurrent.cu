@@ -60,6 +60,7 @@ struct MatRecParams {
     const int* cu_q;            // [rows + 1]
     float* out;                 // [N, H * V] float
     int H, D, V, head_stride, normaliser, act, vec_ok;
+    int qk_rep = 1;             // heads that share one head of q and k: head h reads q / k head h / qk_rep
     float q_scale, denom_eps;
 };
 
@@ -113,8 +114,8 @@ __global__ void __launch_bounds__(MR_WARPS * 32) matrix_recurrence_kernel(const 
         const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
         S[i] = (live && d < D) ? (is_norm ? st[(size_t)D * V + d] : st[(size_t)d * V + col]) : 0.f;
     }
-    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)head * D;
-    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)head * D;
+    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)(head / p.qk_rep) * D;
+    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)(head / p.qk_rep) * D;
     const T* vg = reinterpret_cast<const T*>(p.v) + (size_t)head * V;
     const float decay_const = p.decay_head ? p.decay_head[head] : 1.f;
 
@@ -275,8 +276,8 @@ __global__ void __launch_bounds__(128) matrix_step_kernel(const MatRecParams p) 
     const int D = p.D, V = p.V;
     const int tok = blockIdx.z, head = blockIdx.y;   // (row r brings token r)
     const float bt = p.b ? p.b[(size_t)tok * p.H + head] : 1.f;
-    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)tok * p.ldq + (size_t)head * D;
-    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)tok * p.ldk + (size_t)head * D;
+    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)tok * p.ldq + (size_t)(head / p.qk_rep) * D;
+    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)tok * p.ldk + (size_t)(head / p.qk_rep) * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         qs[d] = in_act(to_f32<T>(qg[d]), p.act) * p.q_scale;
         ks[d] = in_act(to_f32<T>(kg[d]), p.act) * bt;
@@ -568,8 +569,10 @@ EMS_EXPORT int ems_matrix_recurrence(const void* q, long long ldq, const void* k
                                      const float* a, const float* b, const float* denom_floor, float denom_eps,
                                      float* denom, float* state, int head_stride, int normaliser, const int* slots,
                                      const int* cu_q, int rows, int N, int H, int D, int V, float* out,
-                                     cudaStream_t stream) {
+                                     int qk_heads, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return EMS_OK;
+    if (qk_heads <= 0) qk_heads = H;   // (every head has q and k of its own)
+    if (H % qk_heads) return EMS_ERR_SHAPE;
     if (H <= 0 || D <= 0 || V <= 0 || (!decay_head && !a) || (normaliser && (!denom || !denom_floor)) ||
         head_stride < D * V + (normaliser ? D : 0) || H > 65535 || rows > 65535)
         return EMS_ERR_SHAPE;
@@ -577,7 +580,7 @@ EMS_EXPORT int ems_matrix_recurrence(const void* q, long long ldq, const void* k
     p.q = q; p.k = k; p.v = v; p.ldq = ldq; p.ldk = ldk; p.ldv = ldv; p.decay_head = decay_head; p.a = a; p.b = b;
     p.denom_floor = denom_floor; p.denom = denom; p.state = state; p.slots = slots; p.cu_q = cu_q; p.out = out;
     p.H = H; p.D = D; p.V = V; p.head_stride = head_stride; p.normaliser = normaliser; p.act = act;
-    p.q_scale = q_scale; p.denom_eps = denom_eps;
+    p.q_scale = q_scale; p.denom_eps = denom_eps; p.qk_rep = H / qk_heads;
     if (dtype == EMS_F32) return launch_matrix_recurrence<float>(p, rows, N, stream);
     if (dtype == EMS_BF16) return launch_matrix_recurrence<bf16>(p, rows, N, stream);
     return EMS_ERR_DTYPE;

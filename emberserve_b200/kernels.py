@@ -77,11 +77,11 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_glu_act": [P, L, P, I, I, I, I, F, F, I, P],
         "ems_causal_taps": [P, L, P, I, P, I, P, P, P, P, P, I, I, I, I, I, P],
         "ems_paged_attention_masked": [P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, I, P, P, L, F, I, I,
-                                       P, L, I, I, I, P, I, P, P],
+                                       P, L, I, I, I, P, I, P, F, P],
         "ems_unary_act": [P, P, I, L, I, P],
-        "ems_qk_prep": [P, L, I, I, I, I, I, P, P, P, I, I, I, F, P, P, P, I, I, I, I, I, I, F, P, I, P],
+        "ems_qk_prep": [P, L, I, I, I, I, I, P, P, P, I, I, I, F, P, P, P, I, I, I, I, I, I, F, P, I, P, P, I, I, P],
         "ems_norm_mean2": [P, P, P, P, I, P, I, I, I, F, P],
-        "ems_matrix_recurrence": [P, L, P, L, P, L, I, I, F, P, P, P, P, F, P, P, I, I, P, P, I, I, I, I, I, P, P],
+        "ems_matrix_recurrence": [P, L, P, L, P, L, I, I, F, P, P, P, P, F, P, P, I, I, P, P, I, I, I, I, I, P, I, P],
         "ems_mlstm_gates": [P, P, P, I, F, P, I, I, P, P, I, I, P, P, P, P],
         "ems_group_norm_gate": [P, P, P, I, P, L, P, I, I, I, I, F, P],
         "ems_rglru_scan": [P, P, P, P, P, I, P, L, I, F, P, P, P, P, I, I, I, I, I, P],
@@ -89,17 +89,23 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_rope_inplace": [P, I, I, I, I, I, I, I, I, P, P, P],
         "ems_latent_attention": [P, P, I, I, I, P, P, I, I, P, P, P, I, I, I, I, F, I, P, L, I, P],
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
-        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P, I, P],
+        "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P, I, P, F, F, I, P],
         "ems_moe_down_grouped_tc05": [P, P, P, I, I, I, I, P, P],
         "ems_moe_combine_rows": [P, P, P, P, I, I, I, P, P],
         "ems_moe_gather": [P, P, I, I, I, P, P],
         "ems_moe_up_grouped_tc05": [P, P, P, I, I, I, I, P, P, P, I, F, F, P],
-        "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P, F, F, P],
+        "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P, F, F, I, P],
         "ems_moe_down": [P, P, I, P, P, I, I, I, P, I, P],
-        "ems_moe_combine": [P, P, P, I, I, I, I, P, P],
+        "ems_moe_combine": [P, P, P, I, I, I, I, P, P, P, I, P],
         "ems_add_cast": [P, P, P, I, I, I, P],
         "ems_token_gate": [P, P, I, L, I, P, P, P, I, I, I, P],
         "ems_depth_mix": [P, P, I, F, P, P, P, I, L, I, I, I, P],
+        "ems_add_scaled_norm2": [P, P, P, F, F, F, P, P, P, I, F, F, P, P, I, I, I, P],
+        "ems_stream_norm": [P, P, I, F, F, I, I, P],
+        "ems_softcap": [P, L, F, P],
+        "ems_delta_recurrence": [P, L, P, L, P, L, P, L, I, I, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P, P],
+        "ems_ssm_gates": [P, L, I, P, P, I, P, P, I, I, P],
+        "ems_gate_group_norm": [P, P, L, I, P, P, L, P, I, P, I, I, I, I, I, F, P],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -495,12 +501,14 @@ def moe_max_tiles(num_pairs: int, num_experts: int, tile_rows: int) -> int:
 
 MOE_BIG_TILE_ROWS = 256  # rows of a tile of the tcgen05 grouped product
 MOE_SCORINGS = {"softmax": 0, "sigmoid": 1}
+EXPERT_ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "gelu": 4}  # of experts without a gate ("gelu": the erf form)
 
 
 def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
               offsets: torch.Tensor, perm: torch.Tensor, plan: torch.Tensor, max_tiles: int,
               align: int = 1, big: torch.Tensor | None = None, inv: torch.Tensor | None = None,
-              scoring: str = "softmax") -> None:
+              scoring: str = "softmax", correction: torch.Tensor | None = None, renorm_eps: float = 0.0,
+              scale: float = 1.0, plan_experts: int | None = None) -> None:
     """From router logits [N, E] (float32): softmax over all experts (or, with scoring "sigmoid", the
     sigmoid of every logit by itself), the `top` largest per token
     (ids, weights: [N, top]; the weights are the scores, divided by their sum if `renormalize`),
@@ -510,8 +518,12 @@ def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tens
     rows per tile).  With `align` > 1 (steps of more than 512 tokens) every expert's sorted rows
     start at a multiple of `align`, `perm` (len(big) * align entries) is -1 between them, and `big`
     (int32) receives the expert of every group of `align` rows, -1 where none; `inv` (optional, the
-    same steps) receives the sorted row of every pair."""
+    same steps) receives the sorted row of every pair.  With `correction` (float32 [E]) the experts are
+    chosen by score + correction while the weights stay the scores; `renorm_eps` joins the sum that
+    `renormalize` divides by; `scale` multiplies the weights; experts at and past `plan_experts` get no
+    tiles (they have no weights; `moe_combine` returns their input)."""
     n, e = logits.shape
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == e)
     assert logits.dtype == torch.float32 and weights.dtype == torch.float32
     assert ids.numel() >= n * top and weights.numel() >= n * top and perm.numel() >= n * top
     assert offsets.numel() >= 3 * e + 1 and plan.numel() >= 1 + 3 * max_tiles
@@ -520,7 +532,8 @@ def moe_route(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tens
     _check(library().ems_moe_route(_ptr(logits, "logits"), n, e, top, 1 if renormalize else 0, _i32(ids, "ids"),
                                    _ptr(weights, "weights"), _i32(offsets, "offsets"), _i32(perm, "perm"),
                                    _i32(plan, "plan"), max_tiles, align, _i32(big, "big"), max_big,
-                                   _i32(inv, "inv"), MOE_SCORINGS[scoring], _stream()),
+                                   _i32(inv, "inv"), MOE_SCORINGS[scoring], _ptr(correction, "correction"),
+                                   float(renorm_eps), float(scale), int(plan_experts or 0), _stream()),
            "moe_route", 1 if n <= 512 else 4)
 
 
@@ -558,18 +571,21 @@ def moe_up_grouped_tc05(xs: torch.Tensor, wgu: torch.Tensor, big: torch.Tensor, 
 
 def moe_up(x: torch.Tensor, wgu: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
            max_tiles: int, top: int, act: str, out: torch.Tensor, kernel: str = "auto",
-           in_scale: torch.Tensor | None = None, limit: float = 0.0, alpha: float = 1.0) -> None:
+           in_scale: torch.Tensor | None = None, limit: float = 0.0, alpha: float = 1.0, gated: bool = True) -> None:
     """out[i, :] = act(x[t] Wg[e]^T) * (x[t] Wu[e]^T) for sorted pair i (token t = perm[i] // top) of
     expert e; wgu: [E, 2 * ff, K] with the gate rows first.  bfloat16 runs on the tensor cores where K
     is a multiple of 8; kernel="generic" keeps the CUDA-core kernel.  With `in_scale` (float32, one
     number per pair) the expert reads in_scale[pair] * x[t]: both 32-bit sums are multiplied by it.
-    `limit` and `alpha` are the constants of the activation "swiglu_capped"."""
+    `limit` and `alpha` are the constants of the activation "swiglu_capped".  With `gated` False the experts
+    have no gate: wgu is [E, ff, K] and out[i, :] = act(x[t] Wu[e]^T), act one of `EXPERT_ACTIVATIONS`."""
     e, ff2, k = wgu.shape
-    assert x.shape[1] == k and out.shape[1] * 2 == ff2 and x.dtype == wgu.dtype == out.dtype
+    ff = ff2 // 2 if gated else ff2
+    assert x.shape[1] == k and out.shape[1] == ff and x.dtype == wgu.dtype == out.dtype
+    code = GLU_ACTIVATIONS[act] if gated else EXPERT_ACTIVATIONS[act]
     _check(library().ems_moe_up(_ptr(x, "x"), _ptr(wgu, "wgu"), _dt(x), _i32(perm, "perm"), _i32(plan, "plan"),
-                                max_tiles, top, ff2 // 2, k, GLU_ACTIVATIONS[act], _ptr(out, "out"),
+                                max_tiles, top, ff, k, code, _ptr(out, "out"),
                                 1 if kernel == "generic" else 0, _f32(in_scale, "in_scale"), float(limit),
-                                float(alpha), _stream()), "moe_up")
+                                float(alpha), 1 if gated else 0, _stream()), "moe_up")
 
 
 def moe_down(act: torch.Tensor, wdown: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor, plan: torch.Tensor,
@@ -607,14 +623,19 @@ def moe_combine_rows(y: torch.Tensor, inv: torch.Tensor, weights: torch.Tensor |
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor, top: int,
-                extra: torch.Tensor | None = None) -> None:
+                extra: torch.Tensor | None = None, ids: torch.Tensor | None = None, x: torch.Tensor | None = None,
+                num_real: int = 0) -> None:
     """out[t, :] = sum_k weights[t, k] * y[t * top + k, :] (k ascending; every weight 1 when `weights` is
-    None) + extra[t, :] (optional, of out's type)."""
+    None) + extra[t, :] (optional, of out's type).  With `ids` ([N * top] int32), `x` ([N, H], of out's type)
+    and `num_real`, a choice whose expert id is at or past `num_real` contributes x[t] instead of its row of y
+    (an expert that returns its input)."""
     n, h = out.shape
     assert y.dtype == torch.float32 and y.shape[1] == h and (weights is None or weights.dtype == torch.float32)
     assert extra is None or (extra.dtype == out.dtype and extra.shape == out.shape)
+    assert x is None or (ids is not None and x.dtype == out.dtype and x.shape == out.shape and x.is_contiguous())
     _check(library().ems_moe_combine(_ptr(y, "y"), _ptr(weights, "weights"), _ptr(out, "out"), _dt(out), n, top, h,
-                                     _ptr(extra, "extra"), _stream()), "moe_combine")
+                                     _ptr(extra, "extra"), None if x is None else _i32(ids, "ids"), _ptr(x, "x"),
+                                     int(num_real), _stream()), "moe_combine")
 
 
 def attention_scratch_bytes(num_tokens: int, num_heads: int, head_dim: int, splits: int) -> int:
@@ -683,7 +704,7 @@ def decode_attention_fused(qkv: torch.Tensor, out: torch.Tensor, kcache: torch.T
 # ---------------------------------------------------------------------------------------
 # ungated feed-forward, prepared attention heads, masked attention, recurrent mixers
 
-UNARY_ACTIVATIONS = {"relu": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3}
+UNARY_ACTIVATIONS = {"relu": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3, "gelu": 4}  # "gelu": the erf form
 
 
 def unary_act(x: torch.Tensor, out: torch.Tensor, act: str) -> None:
@@ -697,7 +718,8 @@ def qk_prep(proj: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int
             row_of_token: torch.Tensor, table: torch.Tensor | None, rot_dims: int, pairing: str,
             norm_eps: float | None, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
             values_are_keys: bool, write: bool = True, v_norm_eps: float | None = None,
-            v_table: torch.Tensor | None = None, v_pairing: str = "half") -> None:
+            v_table: torch.Tensor | None = None, v_pairing: str = "half", q_gain: torch.Tensor | None = None,
+            k_gain: torch.Tensor | None = None, norm_first: bool = False) -> None:
     """The tokens of a step for attention over a paged cache.  proj: [N, >= (nh + nkv (+ nkv)) * D]
     holds [q | k | v] per row (no v when `values_are_keys`: the value of a token is then its key as
     projected).  Every head of q and k is rotated by the table rows of `positions` on its first
@@ -705,8 +727,13 @@ def qk_prep(proj: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int
     place, k and v go to the token's page slot.  caches: [pages, nkv, page_size, D]; the value cache may
     have another last dimension DV (the v columns of `proj` are then nkv * DV wide).  With `v_norm_eps`
     every value head is divided by its root mean square, and with `v_table` ([positions, DV / 2, 2]) it
-    is turned by the token's position over its whole length, before it is cached."""
+    is turned by the token's position over its whole length, before it is cached.  With `norm_first`
+    the norm of q and k comes BEFORE their rotation; `q_gain` / `k_gain` ([head_dim], shared by the heads, of
+    one type) multiply the normed heads."""
     n = proj.shape[0]
+    assert (q_gain is None) == (k_gain is None)
+    assert q_gain is None or (q_gain.numel() == k_gain.numel() == head_dim and q_gain.dtype == k_gain.dtype
+                              and norm_eps is not None)
     dv = vcache.shape[3]
     cols = (num_heads + num_kv_heads) * head_dim + (0 if values_are_keys else num_kv_heads * dv)
     assert proj.stride(1) == 1 and proj.shape[1] >= cols
@@ -722,7 +749,8 @@ def qk_prep(proj: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int
         float(norm_eps or 0.0), _ptr(kcache, "kcache"), _ptr(vcache, "vcache"), _i32(block_tables, "block_tables"),
         block_tables.shape[1], kcache.shape[2], 1 if values_are_keys else 0, 1 if write else 0, dv,
         0 if v_norm_eps is None else 1, float(v_norm_eps or 0.0), _ptr(v_table, "v_table"),
-        ROTARY_PAIRINGS[v_pairing], _stream()), "qk_prep")
+        ROTARY_PAIRINGS[v_pairing], _ptr(q_gain, "q_gain"), _ptr(k_gain, "k_gain"),
+        0 if q_gain is None else _dt(q_gain), 1 if norm_first else 0, _stream()), "qk_prep")
 
 
 def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -733,7 +761,7 @@ def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Ten
                            gate: torch.Tensor | None = None, splits: int = 1,
                            scratch: torch.Tensor | None = None, kernel: str = "auto", keep_first: int = 0,
                            out_table: torch.Tensor | None = None, out_pairing: str = "half",
-                           positions: torch.Tensor | None = None) -> None:
+                           positions: torch.Tensor | None = None, softcap: float | None = None) -> None:
     """`paged_attention` with three optional extras: `chunk` (the query at position p sees key j <= p
     only if j // chunk == p // chunk, chunks counted from position 0 of the request), `sinks`
     (float32 [nh]: exp(sinks[h]) is added to head h's softmax denominator; it has no value) and
@@ -742,7 +770,7 @@ def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Ten
     beside the window or chunk); a value cache whose last dimension DV differs from head_dim (out is
     then [N, nh * DV]); `out_table` ([positions, DV / 2, 2]: the values were turned by their positions
     when they were cached, and each head's result is turned back by the query's position, positions[n]
-    of token n)."""
+    of token n); `softcap` (a scaled score s enters the softmax as softcap * tanh(s / softcap))."""
     assert q.stride(1) == 1 and out.is_contiguous() and q.dtype == out.dtype == kcache.dtype
     page_size = kcache.shape[2]
     dv = vcache.shape[3]
@@ -761,7 +789,8 @@ def paged_attention_masked(q: torch.Tensor, out: torch.Tensor, kcache: torch.Ten
         None if gate is None else gate.data_ptr(), 0 if gate is None else gate.stride(0), float(scale), max_q_len,
         splits, _ptr(scratch, "scratch"), 0 if scratch is None else scratch.numel() * scratch.element_size(),
         _ATTENTION_IMPL[kernel], int(keep_first or 0), dv, _ptr(out_table, "out_table"),
-        ROTARY_PAIRINGS[out_pairing], None if positions is None else _i32(positions, "positions"), _stream()),
+        ROTARY_PAIRINGS[out_pairing], None if positions is None else _i32(positions, "positions"),
+        float(softcap or 0.0), _stream()),
         "paged_attention_masked", 2 if splits > 1 else 1)
 
 
@@ -790,7 +819,7 @@ def matrix_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, num_hea
                       out: torch.Tensor, act: str = "none", q_scale: float = 1.0,
                       decay_head: torch.Tensor | None = None, a: torch.Tensor | None = None,
                       b: torch.Tensor | None = None, denom_floor: torch.Tensor | None = None,
-                      denom: torch.Tensor | None = None, denom_eps: float = 0.0) -> None:
+                      denom: torch.Tensor | None = None, denom_eps: float = 0.0, qk_heads: int | None = None) -> None:
     """A matrix memory per head, run over every request's tokens in order:
 
         S_t = a_t S_(t-1) + b_t k_t v_t^T,        out_t = S_t^T (q_t * q_scale)
@@ -799,7 +828,8 @@ def matrix_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, num_hea
     through `act` first; a_t is `decay_head[h]` for every token or `a[t, h]`; b_t is `b[t, h]` or 1.
     state: float32 [slots, H, per_head] holding S ([dim, vdim]) and, when `denom` is given, the
     normaliser n_t = a_t n_(t-1) + b_t k_t ([dim]) behind it; then denom[t, h] = max(|n_t . q_t|,
-    denom_floor[t, h]) + denom_eps.  out: float32 [N, H * vdim], not yet divided."""
+    denom_floor[t, h]) + denom_eps.  out: float32 [N, H * vdim], not yet divided.  With `qk_heads` (a
+    divisor of H) q and k have that many heads and head h reads q / k head h // (H / qk_heads)."""
     n = q.shape[0]
     assert q.stride(1) == k.stride(1) == v.stride(1) == 1 and q.dtype == k.dtype == v.dtype
     assert out.dtype == torch.float32 and out.shape == (n, num_heads * vdim) and state.dtype == torch.float32
@@ -812,7 +842,7 @@ def matrix_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, num_hea
         MEMORY_INPUT_ACTIVATIONS[act], float(q_scale), _f32(decay_head, "decay_head"), _f32(a, "a"), _f32(b, "b"),
         _f32(denom_floor, "denom_floor"), float(denom_eps), _f32(denom, "denom"), _ptr(state, "state"),
         state.shape[2], 0 if denom is None else 1, _i32(slots, "slots"), _i32(cu_q, "cu_q"), num_rows, n,
-        num_heads, dim, vdim, _ptr(out, "out"), _stream()), "matrix_recurrence")
+        num_heads, dim, vdim, _ptr(out, "out"), int(qk_heads or 0), _stream()), "matrix_recurrence")
 
 
 def mlstm_gates(pre: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, state: torch.Tensor,
@@ -871,6 +901,115 @@ def rglru_scan(u: torch.Tensor, pre: torch.Tensor, bias_r: torch.Tensor, bias_i:
         _dt(lam), y.data_ptr(), y.stride(0), 1 if y_act else 0, float(cmul), _ptr(state, "state"),
         _i32(slots, "slots"), _i32(cu_q, "cu_q"), _ptr(out, "out"), _dt(out), num_rows, n, c, blocks, _stream()),
         "rglru_scan")
+
+
+def add_scaled_norm2(deltas: "list[tuple[torch.Tensor, float]]", residual: torch.Tensor, gain1: torch.Tensor | None,
+                     gain2: torch.Tensor | None, gain_offset: float, eps: float, out1: torch.Tensor | None,
+                     out2: torch.Tensor | None) -> None:
+    """residual += sum_i scale_i * delta_i (up to three pairs (delta, scale); 32-bit sum), then with r =
+    rsqrt(mean(residual^2) + eps): out1 = residual r (gain1 + gain_offset), out2 = residual r (gain2 +
+    gain_offset); either output may be None (then no norm is computed for it)."""
+    n, c = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and len(deltas) <= 3
+    outs = [o for o in (out1, out2) if o is not None]
+    dt = outs[0].dtype if outs else (deltas[0][0].dtype if deltas else torch.float32)
+    for d, _ in deltas:
+        assert d.shape == (n, c) and d.dtype == dt and d.is_contiguous()
+    for o, g in ((out1, gain1), (out2, gain2)):
+        assert o is None or (o.shape == (n, c) and o.dtype == dt and o.is_contiguous() and g is not None and g.numel() == c)
+    gains = [g for g in (gain1, gain2) if g is not None]
+    assert len({g.dtype for g in gains}) <= 1
+    if not residual.is_cuda:
+        raise KernelError("residual must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    ds = [d for d, _ in deltas] + [None] * (3 - len(deltas))
+    sc = [float(x) for _, x in deltas] + [0.0] * (3 - len(deltas))
+    _check(library().ems_add_scaled_norm2(
+        _ptr(ds[0], "delta"), _ptr(ds[1], "delta"), _ptr(ds[2], "delta"), sc[0], sc[1], sc[2], _ptr(residual, "residual"),
+        _ptr(gain1 if out1 is not None else None, "gain1"), _ptr(gain2 if out2 is not None else None, "gain2"),
+        _dt(gains[0]) if gains else 0, float(gain_offset), float(eps), _ptr(out1, "out1"), _ptr(out2, "out2"),
+        0 if dt == torch.float32 else 1, n, c, _stream()), "add_scaled_norm2")
+
+
+def stream_norm(residual: torch.Tensor, gain: torch.Tensor, gain_offset: float, eps: float) -> None:
+    """residual <- residual / sqrt(mean(residual^2) + eps) * (gain + gain_offset), in place, 32-bit."""
+    n, c = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and gain.numel() == c
+    if not residual.is_cuda:
+        raise KernelError("residual must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_stream_norm(_ptr(residual, "residual"), _ptr(gain, "gain"), _dt(gain), float(gain_offset),
+                                     float(eps), n, c, _stream()), "stream_norm")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    if not x.is_cuda:
+        raise KernelError("x must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_softcap(_ptr(x, "x"), x.numel(), float(cap), _stream()), "softcap")
+
+
+def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, g_raw: torch.Tensor,
+                     g_bias: torch.Tensor, a_log: torch.Tensor, num_heads: int, qk_heads: int, dim: int, vdim: int,
+                     state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, num_rows: int, out: torch.Tensor,
+                     act: str = "silu", unit_eps: float | None = 1e-6, q_scale: float = 1.0) -> None:
+    """A matrix memory per head written by the delta rule with a decay per key channel, run over every
+    request's tokens in order:
+
+        S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   out_t = S^T q_t
+
+    q, k: [N, >= qk_heads * dim], v: [N, >= H * vdim], beta: [N, >= H] (column ranges of wider buffers are
+    fine), each of q, k, v passed through `act`; with `unit_eps` q and k become x / sqrt(sum(x^2) + unit_eps)
+    per head; q is multiplied by `q_scale`; beta_t = sigmoid(beta[t, h]); g_t = exp(-exp(a_log[h]) *
+    softplus(g_raw[t, h * dim + d] + g_bias[h * dim + d])) with g_raw float32 [N, H * dim].  Head h reads
+    q / k head h // (H / qk_heads).  state: float32 [slots, H, dim * vdim]; out: float32 [N, H * vdim]."""
+    n = q.shape[0]
+    assert q.stride(1) == k.stride(1) == v.stride(1) == beta.stride(1) == 1 and q.dtype == k.dtype == v.dtype == beta.dtype
+    assert out.dtype == torch.float32 and out.shape == (n, num_heads * vdim) and out.is_contiguous()
+    assert state.dtype == torch.float32 and state.dim() == 3 and state.shape[1:] == (num_heads, dim * vdim)
+    assert g_raw.dtype == torch.float32 and g_raw.shape == (n, num_heads * dim) and g_raw.is_contiguous()
+    assert g_bias.numel() == num_heads * dim and a_log.numel() == num_heads and g_bias.dtype == a_log.dtype
+    if not q.is_cuda:
+        raise KernelError("q must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_delta_recurrence(
+        q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), beta.data_ptr(),
+        beta.stride(0), _dt(q), MEMORY_INPUT_ACTIVATIONS[act], 0 if unit_eps is None else 1, float(unit_eps or 0.0),
+        float(q_scale), _f32(g_raw, "g_raw"), _ptr(g_bias, "g_bias"), _ptr(a_log, "a_log"), _dt(a_log),
+        _ptr(state, "state"), _i32(slots, "slots"), _i32(cu_q, "cu_q"), num_rows, n, num_heads, qk_heads, dim, vdim,
+        _ptr(out, "out"), _stream()), "delta_recurrence")
+
+
+def ssm_gates(x: torch.Tensor, bias: torch.Tensor, a_log: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> None:
+    """dt = softplus(x[t, h] + bias[h]); a[t, h] = exp(-exp(a_log[h]) * dt); b[t, h] = dt (float32 [N, H]).
+    x: [N, H], may be a column range of a wider buffer."""
+    n, h = x.shape
+    assert x.stride(1) == 1 and a.shape == b.shape == (n, h) and a.dtype == b.dtype == torch.float32
+    assert a.is_contiguous() and b.is_contiguous() and bias.numel() == a_log.numel() == h and bias.dtype == a_log.dtype
+    if not x.is_cuda:
+        raise KernelError("x must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_ssm_gates(x.data_ptr(), x.stride(0), _dt(x), _ptr(bias, "bias"), _ptr(a_log, "a_log"),
+                                   _dt(a_log), _f32(a, "a"), _f32(b, "b"), n, h, _stream()), "ssm_gates")
+
+
+def gate_group_norm(o: torch.Tensor, groups: int, eps: float, weight: torch.Tensor, out: torch.Tensor,
+                    z: torch.Tensor | None = None, skip: torch.Tensor | None = None, x: torch.Tensor | None = None,
+                    x_act: str = "none", head_width: int | None = None) -> None:
+    """y = (o + skip[h] * act(x)) * silu(z); out = y / rms_g(y) * weight: the gate comes BEFORE the norm.
+    o: float32 [N, C]; x, z: [N, >= C] of out's type (column ranges are fine); skip: [C / head_width] of
+    weight's type, head h owning the columns [h * head_width, (h + 1) * head_width); each of `groups` equal
+    consecutive parts of a row is divided by its own root mean square.  z and skip are optional."""
+    n, c = o.shape
+    hv = int(head_width or c)
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.shape == (n, c) and weight.numel() == c
+    assert z is None or (z.dtype == out.dtype and z.stride(1) == 1 and z.shape[1] >= c)
+    assert skip is None or (x is not None and x.dtype == out.dtype and x.stride(1) == 1 and x.shape[1] >= c
+                            and skip.dtype == weight.dtype and skip.numel() * hv == c)
+    if not o.is_cuda:
+        raise KernelError("o must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    _check(library().ems_gate_group_norm(
+        _f32(o, "o"), None if x is None else x.data_ptr(), 0 if x is None else x.stride(0),
+        MEMORY_INPUT_ACTIVATIONS[x_act], _ptr(skip, "skip"), None if z is None else z.data_ptr(),
+        0 if z is None else z.stride(0), _ptr(weight, "weight"), _dt(weight), _ptr(out, "out"), _dt(out), n, c,
+        groups, hv, float(eps), _stream()), "gate_group_norm")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -214,6 +214,27 @@ class NormedDelta:
 
 
 @dataclass
+class ScaledSum:
+    """What a block leaves to be added to the residual stream when it is a weighted sum of several
+    sub-layer outputs: ``sum_i scale_i * x_i``.  The norm kernel that receives it adds every term into the
+    32-bit residual itself, so the sum is never rounded to the activation type.  `terms` holds at most
+    three (tensor, scale) pairs."""
+
+    terms: "list[tuple[torch.Tensor, float]]"
+
+    def scaled(self, factor: float) -> "ScaledSum":
+        return ScaledSum([(x, s * factor) for x, s in self.terms])
+
+    @property
+    def shape(self):
+        return self.terms[0][0].shape
+
+    @property
+    def dtype(self):
+        return self.terms[0][0].dtype
+
+
+@dataclass
 class ScaledRows:
     """Activations of a norm that is not finished yet: `x` holds residual * gain (activation
     dtype); row n still has to be multiplied by rsqrt(sumsq[:parts, n].sum() / width + eps).
@@ -303,6 +324,10 @@ class Part:
 
 
 class Norm(Part):
+    def normalize_stream(self, residual: torch.Tensor, ctx: "StepContext") -> None:
+        """Norm the 32-bit stream itself, in place (a norm that stands behind the embedding)."""
+        raise NotImplementedError(f"{type(self).__name__} cannot norm the stream in place")
+
     def split_request(self, residual: torch.Tensor, ctx: StepContext) -> "NormRequest | None":
         """A `NormRequest` if, in this step, the norm can be begun by the product before it and
         finished by the product behind it (then `forward` will be handed the `ScaledRows` that

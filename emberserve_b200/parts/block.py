@@ -5,6 +5,9 @@ behind the sub-layers a block may run parts that act on the stream itself (``str
 Sandwich (a norm before AND behind every sub-layer, optionally a short convolution before the
 mixer, optionally no feed-forward): ``h += norm1b(mixer(conv(norm1(h)))); h += norm2b(ffn(norm2(h)))``.
 
+Shared-input (``SharedInputBlock``): both sub-layers read norms of the SAME stream and their outputs join it
+together, times a constant: ``h += m * (mixer(norm1(h)) + ffn(norm2(h)))``.
+
 Written on the pair (delta, residual) so that each norm performs the add that precedes
 it (``emberserve/model/qwen2.py:122-164``): the block receives the previous block's
 output `delta`, which has not been added to the stream yet, and returns its own.
@@ -17,8 +20,9 @@ from typing import Any
 
 import torch
 
-from emberserve_b200.parts.base import (Block, CacheNeed, NormedDelta, Part, StepContext, StreamPart, build_part,
-                                        register_part)
+from emberserve_b200 import kernels as K
+from emberserve_b200.parts.base import (Block, CacheNeed, NormedDelta, Part, ScaledSum, StepContext, StreamPart,
+                                        build_part, register_part)
 
 
 @dataclass(frozen=True)
@@ -160,3 +164,77 @@ class SandwichBlock(Block):
             return a
         y = self.ffn_norm.forward(a, residual, ctx)
         return NormedDelta(self.ffn.forward(y, ctx), self.ffn_post_norm)
+
+
+@dataclass(frozen=True)
+class SharedInputBlockSpec:
+    mixer: Any
+    mixer_norm: Any  # spec of a one-group RMS norm ("rmsnorm_grouped")
+    feed_forward: Any | None = None  # None: the block is its mixer alone
+    ffn_norm: Any | None = None
+    residual_mult: float = 1.0  # m: what the block adds to the stream is multiplied by it
+    kind: str = "shared_input"
+
+
+@register_part("block", "shared_input")
+class SharedInputBlock(Block):
+    """``h += m * (mixer(norm1(h)) + ffn(norm2(h)))``: the two norms differ in their gains only, so one
+    kernel adds what the block before left (a tensor or a `ScaledSum`) into the 32-bit stream, takes
+    the root mean square once and writes both normed inputs.  The block hands its own outputs on as a
+    `ScaledSum`, unrounded: a mixer may itself return a `ScaledSum` (two mixers side by side with
+    weights), whose terms are then multiplied by m."""
+
+    def __init__(self, spec: SharedInputBlockSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, prefix + ".mixer_norm", self.shared)
+        self.mixer = build_part("mixer", spec.mixer, prefix + ".mixer", self.shared)
+        self.ffn = self.ffn_norm = None
+        if spec.feed_forward is not None:
+            if spec.ffn_norm is None:
+                raise ValueError(f"{prefix}: a feed-forward needs its norm")
+            self.ffn_norm = build_part("norm", spec.ffn_norm, prefix + ".ffn_norm", self.shared)
+            self.ffn = build_part("feed_forward", spec.feed_forward, prefix + ".ffn", self.shared)
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and (getattr(norm.spec, "kind", None) != "rmsnorm_grouped" or norm.spec.groups != 1):
+                raise ValueError(f"{prefix}: the two norms share their statistics, so each is a one-group RMS norm")
+        if self.ffn_norm is not None and (self.ffn_norm.spec.eps != self.mixer_norm.spec.eps
+                                          or self.ffn_norm.spec.gain_offset != self.mixer_norm.spec.gain_offset):
+            raise ValueError(f"{prefix}: the two norms must agree in eps and gain offset")
+
+    def children(self) -> dict[str, Part]:
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.ffn is not None:
+            out.update(ffn_norm=self.ffn_norm, ffn=self.ffn)
+        return out
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def scratch_elements_per_token(self) -> int:
+        return 2 * self.mixer_norm.spec.dim
+
+    def forward(self, delta, residual: torch.Tensor, ctx: StepContext, cache: Any):
+        ctx.extra.pop("next_norm", None)
+        ctx.extra["norm_behind"] = None
+        ns = self.mixer_norm.spec
+        if delta is None:
+            terms = []
+        elif isinstance(delta, ScaledSum):
+            terms = delta.terms
+        elif isinstance(delta, torch.Tensor):
+            terms = [(delta, 1.0)]
+        else:
+            raise TypeError(f"{self.prefix}: cannot take a delta of type {type(delta).__name__}")
+        n = residual.shape[0]
+        x1 = ctx.scratch("normed", (n, ns.dim), ctx.dtype)
+        x2 = ctx.scratch("normed_second", (n, ns.dim), ctx.dtype) if self.ffn is not None else None
+        K.add_scaled_norm2(terms, residual, self.mixer_norm.weight, None if self.ffn is None else self.ffn_norm.weight,
+                           ns.gain_offset, ns.eps, x1, x2)
+        m = float(self.spec.residual_mult)
+        a = self.mixer.forward(x1, ctx, cache)
+        out = a.scaled(m) if isinstance(a, ScaledSum) else ScaledSum([(a, m)])
+        if self.ffn is not None:
+            out = ScaledSum(out.terms + [(self.ffn.forward(x2, ctx), m)])
+        if len(out.terms) > 3:
+            raise ValueError(f"{self.prefix}: at most three terms join the stream at once")
+        return out

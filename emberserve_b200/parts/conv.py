@@ -25,6 +25,9 @@ class CausalTapsSpec:
     kind: str = "causal_taps"
     identity: bool = True  # add the input to the convolution's output
     bias_name: str | None = None  # checkpoint tensor [width]
+    # the weight as several checkpoint tensors stacked along the channels: (name, first channel, end);
+    # when given, `weight_name` only labels the part
+    weight_parts: tuple = ()
 
 
 @register_part("conv", "causal_taps")
@@ -39,7 +42,9 @@ class CausalTaps(Part):
 
     def param_specs(self) -> dict[str, ParamSpec]:
         s: CausalTapsSpec = self.spec
-        specs = {"weight": ParamSpec((s.width, s.taps), [Source(s.weight_name)])}
+        sources = ([Source(name, (lo, hi)) for name, lo, hi in s.weight_parts] if s.weight_parts
+                   else [Source(s.weight_name)])
+        specs = {"weight": ParamSpec((s.width, s.taps), sources)}
         if s.bias_name is not None:
             specs["bias"] = ParamSpec((s.width,), [Source(s.bias_name)], init="bias")
         return specs

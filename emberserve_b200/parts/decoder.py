@@ -63,6 +63,8 @@ class DecoderSpec:
     # each is [rows, hidden].  `StreamInject` names them.
     tables: dict[str, tuple[str, int]] = field(default_factory=dict)
     embed_scale: float = 1.0  # the embedding row is multiplied by this as it enters the 32-bit stream
+    embed_norm: Any | None = None  # norm spec: the stream is normed in place right behind the embedding
+    logit_softcap: float | None = None  # logits <- cap * tanh(logits / cap)
 
 
 class Decoder:
@@ -72,6 +74,8 @@ class Decoder:
         self.blocks: list[Block] = [
             build_part("block", b, f"layers.{i}", self.shared) for i, b in enumerate(spec.layers)]
         self.final_norm = build_part("norm", spec.final_norm, "final_norm", self.shared)
+        self.embed_norm = (build_part("norm", spec.embed_norm, "embed_norm", self.shared)
+                           if spec.embed_norm is not None else None)
         self.embed_position = (self.shared.get("position", spec.embedding_position)
                                if spec.embedding_position is not None else None)
         self.embed: torch.Tensor | None = None
@@ -132,6 +136,8 @@ class Decoder:
         for i, b in enumerate(self.blocks):
             rec(f"layers.{i}", b)
         rec("final_norm", self.final_norm)
+        if self.embed_norm is not None:
+            rec("embed_norm", self.embed_norm)
         for j, p in enumerate(self.shared.all()):
             rec(f"shared.{j}", p)
         return out
@@ -207,6 +213,8 @@ class Decoder:
         K.embedding(self.embed, ctx.tokens, residual, deferred=ctx.deferred, scale=s.embed_scale)
         if self.embed_position is not None:
             self.embed_position.on_embedding(residual, ctx)
+        if self.embed_norm is not None:
+            self.embed_norm.normalize_stream(residual, ctx)
         delta = None
         for i, (call, handle) in enumerate(zip(s.order, handles, strict=True)):
             # the norm that will receive this block's output, if it can be begun by the block's
@@ -229,4 +237,6 @@ class Decoder:
         assert want_rows is not None and want_rows.numel() == num_want
         normed = self.final_norm.forward(delta, residual, ctx, rows=want_rows)
         linear_f32_out(normed, self.head, logits)
+        if s.logit_softcap:
+            K.softcap(logits, s.logit_softcap)
         return logits

@@ -9,6 +9,8 @@ every token uses `top_k`.
     y = sum_k Wd[e_k] glu(Wg[e_k] (weight_k h), Wu[e_k] (weight_k h))     with `weight_on_input`
 
 With `shared_expert`, the spec of a dense feed-forward that every token uses, its output is added.
+``RoutedMLP`` (below) is the form whose experts have no gate, with identity experts, a correction on the
+choice and a constant on the weights.
 
 The (token, choice) pairs are sorted by expert on the device and the experts run as two grouped
 matrix products over the sorted rows (``csrc/moe_routed.cu``); nothing is read back to the host,
@@ -153,4 +155,120 @@ class RoutedGLU(FeedForward):
         K.moe_down(act, self.wdown.view(e, s.hidden, s.intermediate), perm, offsets, plan, max_tiles, y)
         out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
         K.moe_combine(y, None if s.weight_on_input else weights, out, top, extra=extra)
+        return out
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    hidden: int
+    intermediate: int  # of one expert
+    num_experts: int  # experts with weights
+    top_k: int
+    router_name: str  # checkpoint tensor [num_experts + identity_experts, hidden]
+    expert_names: tuple[tuple[str, str], ...]  # per expert with weights, its up and down projections
+    activation: str = "gelu"  # one of kernels.EXPERT_ACTIVATIONS
+    identity_experts: int = 0  # further router outputs whose expert returns its input
+    correction_name: str | None = None  # [num_experts + identity_experts]: added to the scores for the choice only
+    renormalize: bool = True  # the chosen scores are divided by (their sum + renorm_eps)
+    renorm_eps: float = 1e-20
+    route_scale: float = 1.0  # multiplies the weights
+    shared_expert: Any = None  # spec of a feed-forward that runs for every token and is added
+    kind: str = "routed_mlp"
+
+
+@register_part("feed_forward", "routed_mlp")
+class RoutedMLP(FeedForward):
+    """Routed experts without a gate: ``expert_e(h) = Wd[e] act(Wu[e] h)``.
+
+        z = Wr h                      router logits over the experts AND the identity experts, 32-bit
+        s = softmax(z)
+        chosen = the top_k largest of s + correction       (the weights use s alone)
+        weight = s[chosen] / (sum + renorm_eps) * route_scale
+        y = sum_k weight_k * (h if e_k is an identity expert else expert_(e_k)(h))  (+ shared expert)
+
+    Routing, the sort by expert, the two grouped products and the combine step are the kernels of
+    ``RoutedGLU`` (``csrc/moe_routed.cu``) in their ungated form; identity experts get no tiles and the
+    combine step adds the token's own input for them."""
+
+    router: torch.Tensor
+    wup: torch.Tensor  # [E * ff, hidden]
+    wdown: torch.Tensor  # [E * hidden, ff]
+    correction: torch.Tensor | None = None
+
+    def __init__(self, spec: RoutedMLPSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        self.total = spec.num_experts + spec.identity_experts
+        if spec.num_experts < 1 or spec.identity_experts < 0 or not 1 <= spec.top_k <= self.total:
+            raise ValueError(f"top_k={spec.top_k} of {spec.num_experts} experts and {spec.identity_experts} "
+                             f"identity experts")
+        if len(spec.expert_names) != spec.num_experts:
+            raise ValueError("one (up, down) name pair per expert is needed")
+        if spec.activation not in K.EXPERT_ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r}: one of {sorted(K.EXPERT_ACTIVATIONS)}")
+        self._router32: torch.Tensor | None = None
+        self._correction32: torch.Tensor | None = None
+        self.shared_ffn = (build_part("feed_forward", spec.shared_expert, prefix + ".shared", self.shared)
+                           if spec.shared_expert is not None else None)
+
+    def children(self) -> dict[str, Part]:
+        return {} if self.shared_ffn is None else {"shared": self.shared_ffn}
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: RoutedMLPSpec = self.spec
+        ff, hid = s.intermediate, s.hidden
+        specs = {
+            "router": ParamSpec((self.total, hid), [Source(s.router_name)]),
+            "wup": ParamSpec((s.num_experts * ff, hid),
+                             [Source(u, (e * ff, (e + 1) * ff)) for e, (u, _) in enumerate(s.expert_names)]),
+            "wdown": ParamSpec((s.num_experts * hid, ff),
+                               [Source(d, (e * hid, (e + 1) * hid)) for e, (_, d) in enumerate(s.expert_names)]),
+        }
+        if s.correction_name is not None:
+            specs["correction"] = ParamSpec((self.total,), [Source(s.correction_name)], init="bias")
+        return specs
+
+    def bind(self, params: dict[str, torch.Tensor]) -> None:
+        super().bind(params)
+        self._router32 = self.router.float()  # the logits are a 32-bit product
+        self._correction32 = None if self.correction is None else self.correction.float().contiguous()
+
+    def scratch_elements_per_token(self) -> int:
+        s: RoutedMLPSpec = self.spec
+        return s.top_k * (s.intermediate + 2 * s.hidden) + 4 * s.hidden + 2 * self.total
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        s: RoutedMLPSpec = self.spec
+        n, e, top = x.shape[0], self.total, s.top_k
+        pairs = n * top
+        x32 = x
+        if x.dtype != torch.float32:
+            x32 = ctx.scratch("moe_x32", (n, s.hidden), torch.float32)
+            x32.copy_(x)
+        logits = ctx.scratch("moe_logits", (n, e), torch.float32)
+        torch.mm(x32, self._router32.t(), out=logits)
+        tile = K.moe_tile_rows()
+        max_tiles = K.moe_max_tiles(pairs, e, tile)
+        ids = ctx.scratch("moe_ids", (pairs,), torch.int32)
+        weights = ctx.scratch("moe_weights", (pairs,), torch.float32)
+        offsets = ctx.scratch("moe_offsets", (3 * e + 1,), torch.int32)
+        plan = ctx.scratch("moe_plan", (1 + 3 * max_tiles,), torch.int32)
+        perm = ctx.scratch("moe_perm", (pairs,), torch.int32)
+        extra = None
+        if self.shared_ffn is not None:
+            # (its result stays in a buffer of its own until the routed experts' sum takes it in)
+            extra = ctx.scratch("ffn_shared", (n, s.hidden), ctx.dtype)
+            extra.copy_(self.shared_ffn.forward(x, ctx))
+        K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles,
+                    correction=self._correction32, renorm_eps=s.renorm_eps, scale=s.route_scale,
+                    plan_experts=s.num_experts)
+        act = ctx.scratch("moe_act", (pairs, s.intermediate), ctx.dtype)
+        K.moe_up(x, self.wup.view(s.num_experts, s.intermediate, s.hidden), perm, offsets, plan, max_tiles, top,
+                 s.activation, act, gated=False)
+        y = ctx.scratch("moe_y", (pairs, s.hidden), torch.float32)
+        K.moe_down(act, self.wdown.view(s.num_experts, s.hidden, s.intermediate), perm, offsets, plan, max_tiles, y)
+        out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
+        if s.identity_experts:
+            K.moe_combine(y, weights, out, top, extra=extra, ids=ids, x=x, num_real=s.num_experts)
+        else:
+            K.moe_combine(y, weights, out, top, extra=extra)
         return out

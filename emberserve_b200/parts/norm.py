@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from emberserve_b200 import kernels as K
-from emberserve_b200.parts.base import (Norm, NormedDelta, NormRequest, ParamSpec, ScaledRows, Source,
+from emberserve_b200.parts.base import (Norm, NormedDelta, NormRequest, ParamSpec, ScaledRows, ScaledSum, Source,
                                         StepContext, register_part)
 
 
@@ -78,9 +78,10 @@ class GroupedRMSNorm(Norm):
     consecutive parts g of the vector, then ``y * weight`` over the whole (groups = 1 is the plain
     RMSNorm, with the gain applied to the unrounded 32-bit value).  All of it in 32 bits.
 
-    `forward` takes three kinds of `delta`: None, a tensor (added to the stream as it is), or a
+    `forward` takes these kinds of `delta`: None, a tensor (added to the stream as it is), a
     `NormedDelta` whose own norm is a GroupedRMSNorm: then ``residual += thatnorm(delta.x)`` and
-    this norm of the new residual are one kernel."""
+    this norm of the new residual are one kernel; or a `ScaledSum`, whose terms are added into the
+    32-bit residual first (of every row, also when only some rows are normed)."""
 
     weight: torch.Tensor
 
@@ -101,11 +102,20 @@ class GroupedRMSNorm(Norm):
         # the gain as the kernels read it: with an offset, the 32-bit sum (the stored tensor stays as loaded)
         self.gain = self.weight if not self.spec.gain_offset else self.weight.float() + self.spec.gain_offset
 
+    def normalize_stream(self, residual: torch.Tensor, ctx: StepContext) -> None:
+        s: GroupedRMSNormSpec = self.spec
+        if s.groups != 1:
+            raise NotImplementedError(f"{self.prefix}: the stream is normed in place as one group only")
+        K.stream_norm(residual, self.weight, s.gain_offset, s.eps)
+
     def forward(self, delta, residual: torch.Tensor, ctx: StepContext,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
         s: GroupedRMSNormSpec = self.spec
         n = residual.shape[0] if rows is None else rows.numel()
         out = ctx.scratch("normed" if rows is None else "normed_rows", (n, s.dim), ctx.dtype)
+        if isinstance(delta, ScaledSum):
+            K.add_scaled_norm2(delta.terms, residual, None, None, 0.0, s.eps, None, None)
+            delta = None
         x, gain, groups, eps = delta, None, 1, 0.0
         if isinstance(delta, NormedDelta):
             post = delta.norm

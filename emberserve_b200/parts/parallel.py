@@ -3,6 +3,9 @@ outputs, each first RMS-normed over the model width with a gain of its own:
 
 ``y = (rms(left(x)) * g_left + rms(right(x)) * g_right) / 2``.
 
+With ``combine="weighted"`` there are no norms and no gains: the output is ``left_scale * left(x) + right_scale *
+right(x)``, handed on as a `ScaledSum` so that the block adds both terms into the 32-bit stream itself.
+
 What the pair keeps between steps is what its members keep, side by side (the layer call then
 names one cache entry per member that keeps something).
 """
@@ -15,7 +18,8 @@ from typing import Any
 import torch
 
 from emberserve_b200 import kernels as K
-from emberserve_b200.parts.base import Mixer, ParamSpec, Part, Source, StepContext, build_part, register_part
+from emberserve_b200.parts.base import (Mixer, ParamSpec, Part, ScaledSum, Source, StepContext, build_part,
+                                        register_part)
 
 
 @dataclass(frozen=True)
@@ -23,10 +27,13 @@ class ParallelMixersSpec:
     hidden: int
     left: Any  # mixer specs
     right: Any
-    eps: float
-    left_gain_name: str  # checkpoint tensors [hidden]
-    right_gain_name: str
+    eps: float = 0.0
+    left_gain_name: str | None = None  # checkpoint tensors [hidden] (combine "normed_mean")
+    right_gain_name: str | None = None
     kind: str = "parallel_mixers"
+    combine: str = "normed_mean"  # or "weighted": left_scale * left + right_scale * right
+    left_scale: float = 1.0
+    right_scale: float = 1.0
 
 
 def _as_tuple(need) -> tuple:
@@ -40,6 +47,10 @@ class ParallelMixers(Mixer):
 
     def __init__(self, spec: ParallelMixersSpec, prefix: str, shared=None) -> None:
         super().__init__(spec, prefix, shared)
+        if spec.combine not in ("normed_mean", "weighted"):
+            raise ValueError(f"combine {spec.combine!r}: 'normed_mean' or 'weighted'")
+        if spec.combine == "normed_mean" and (spec.left_gain_name is None or spec.right_gain_name is None):
+            raise ValueError("the normed mean of two mixers needs a gain for each")
         self.left = build_part("mixer", spec.left, prefix + ".left", self.shared)
         self.right = build_part("mixer", spec.right, prefix + ".right", self.shared)
         self._needs = (self.left.cache_need(), self.right.cache_need())
@@ -53,6 +64,8 @@ class ParallelMixers(Mixer):
 
     def param_specs(self) -> dict[str, ParamSpec]:
         s: ParallelMixersSpec = self.spec
+        if s.combine == "weighted":
+            return {}
         return {"left_gain": ParamSpec((s.hidden,), [Source(s.left_gain_name)], init="ones"),
                 "right_gain": ParamSpec((s.hidden,), [Source(s.right_gain_name)], init="ones")}
 
@@ -72,6 +85,12 @@ class ParallelMixers(Mixer):
         s: ParallelMixersSpec = self.spec
         left_cache, right_cache = self._split(cache)
         a = self.left.forward(x, ctx, left_cache)
+        if s.combine == "weighted":
+            # (members of different kinds write to scratch buffers of different names)
+            if type(self.left) is type(self.right):
+                a = ctx.scratch("parallel_left", tuple(a.shape), a.dtype).copy_(a)
+            b = self.right.forward(x, ctx, right_cache)
+            return ScaledSum([(a, float(s.left_scale)), (b, float(s.right_scale))])
         if type(self.left) is type(self.right):  # two parts of one kind share their scratch buffers by name
             a = ctx.scratch("parallel_left", tuple(a.shape), a.dtype).copy_(a)
         b = self.right.forward(x, ctx, right_cache)

@@ -17,6 +17,10 @@
 
 States, gates, decays and every product with a state are 32-bit; the projections and the
 convolution are in the activation type.  Gate pre-activations are products with 32-bit results.
+* ``selective_state_space``: a state space with a scalar decay and step size per head and token, B and C
+  shared by groups of heads, a skip, a gate before a grouped norm (see the class).
+* ``channel_delta``: the delta rule with a decay per head and key channel (see the class).
+
 The same kernels walk a request's tokens in order in prompts, portions and single tokens.
 """
 
@@ -277,3 +281,243 @@ class RGLRU(Mixer):
                      state.slots, ctx.cu_q, ctx.num_rows, out, b)
         y = ctx.scratch("memory_out", (n, s.hidden), ctx.dtype)
         return linear(out, self.wo, None, y, ctx.scratch)
+
+
+def _pad8(n: int) -> int:
+    return -(-n // 8) * 8
+
+
+@dataclass(frozen=True)
+class SelectiveStateSpaceSpec:
+    hidden: int
+    num_heads: int
+    vdim: int  # channels per head
+    state: int  # N: rows of a head's state
+    groups: int  # heads that share one B and C: head h reads group h // (num_heads / groups)
+    norm_groups: int
+    taps: int  # of the convolution over x, B and C; 1 keeps no state
+    eps: float
+    # checkpoint tensors (full names)
+    in_name: str  # [2 inner + 2 groups N + heads, hidden]: z | x | B | C | dt
+    conv_name: str  # [inner + 2 groups N, taps]
+    conv_bias_name: str
+    dt_bias_name: str  # [heads]
+    a_log_name: str  # [heads]
+    d_name: str  # [heads]
+    norm_name: str  # [inner]
+    o_name: str  # [hidden, inner]
+    kind: str = "selective_state_space"
+
+
+@register_part("mixer", "selective_state_space")
+class SelectiveStateSpace(Mixer):
+    """A selective state space with a scalar decay per head (the "state-space duality" form):
+
+        [z | x | B | C | dt] = h Win^T;   (x, B, C) <- silu(conv(x, B, C));   dt <- softplus(dt + dt_bias)
+        S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_t^T,       y_t = S_t^T C_t + D x_t        per head
+        out = (rms_groups(y * silu(z)) * norm) Wo^T
+
+    The recurrence is the matrix memory of ``ems_matrix_recurrence`` with k = B, q = C, v = x, a per-token
+    decay and input scale, and B / C heads shared by groups of heads.  dt, the decay, the state and the
+    gated norm are 32-bit."""
+
+    win: torch.Tensor
+    dt_bias: torch.Tensor
+    a_log: torch.Tensor
+    skip: torch.Tensor
+    norm: torch.Tensor
+    wo: torch.Tensor
+
+    def __init__(self, spec: SelectiveStateSpaceSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.groups <= 0 or spec.num_heads % spec.groups:
+            raise ValueError(f"{spec.num_heads} heads do not split into {spec.groups} groups")
+        if spec.state > 256:
+            raise ValueError(f"state={spec.state}: the memory kernel holds at most 256 rows per head")
+        self.inner = spec.num_heads * spec.vdim
+        if spec.norm_groups <= 0 or self.inner % spec.norm_groups:
+            raise ValueError(f"{self.inner} channels do not split into {spec.norm_groups} norm groups")
+        self.gn = spec.groups * spec.state
+        self.conv_width = self.inner + 2 * self.gn
+        self.dt_at = 2 * self.inner + 2 * self.gn
+        self.rows = self.dt_at + spec.num_heads
+        self.conv = build_part("conv", CausalTapsSpec(self.conv_width, spec.taps, spec.conv_name, identity=False,
+                                                      bias_name=spec.conv_bias_name), prefix + ".conv", self.shared)
+        self._conv_state = self.conv.cache_need()
+
+    def children(self) -> dict[str, Part]:
+        return {"conv": self.conv}
+
+    def cache_need(self):
+        s: SelectiveStateSpaceSpec = self.spec
+        state = FixedState((s.num_heads, s.state * s.vdim), "float32")
+        return state if self._conv_state is None else (self._conv_state, state)
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: SelectiveStateSpaceSpec = self.spec
+        h = s.num_heads
+        return {
+            # (rows past the tensor's, padding to a multiple of 8, stay zero)
+            "win": ParamSpec((_pad8(self.rows), s.hidden), [Source(s.in_name, (0, self.rows))]),
+            "dt_bias": ParamSpec((h,), [Source(s.dt_bias_name)], init="bias"),
+            "a_log": ParamSpec((h,), [Source(s.a_log_name)], init="bias"),
+            "skip": ParamSpec((h,), [Source(s.d_name)], init="ones"),
+            "norm": ParamSpec((self.inner,), [Source(s.norm_name)], init="ones"),
+            "wo": ParamSpec((s.hidden, self.inner), [Source(s.o_name)]),
+        }
+
+    def streamed_params(self) -> list[str]:
+        return ["win", "wo"]
+
+    def scratch_elements_per_token(self) -> int:
+        return _pad8(self.rows) + 3 * self.inner + self.spec.hidden + 4 * self.spec.num_heads
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        s: SelectiveStateSpaceSpec = self.spec
+        n, inner, gn, h = ctx.num_tokens, self.inner, self.gn, s.num_heads
+        conv_cache, state = (None, cache) if self._conv_state is None else cache
+        proj = ctx.scratch("ssm_in", (n, _pad8(self.rows)), ctx.dtype)
+        linear(x, self.win, None, proj, ctx.scratch)
+        xbc = self.conv.forward(proj[:, inner:inner + self.conv_width], ctx, conv_cache)
+        gates = ctx.scratch("ssm_gates", (2, n, h), torch.float32)
+        K.ssm_gates(proj[:, self.dt_at:self.dt_at + h], self.dt_bias, self.a_log, gates[0], gates[1])
+        read = ctx.scratch("memory_read", (n, inner), torch.float32)
+        K.matrix_recurrence(xbc[:, inner + gn:], xbc[:, inner:inner + gn], xbc[:, :inner], h, s.state, s.vdim,
+                            state.state, state.slots, ctx.cu_q, ctx.num_rows, read, act="silu", a=gates[0],
+                            b=gates[1], qk_heads=s.groups)
+        gated = ctx.scratch("memory_gated", (n, inner), ctx.dtype)
+        K.gate_group_norm(read, s.norm_groups, s.eps, self.norm, gated, z=proj[:, :inner], skip=self.skip,
+                          x=xbc[:, :inner], x_act="silu", head_width=s.vdim)
+        y = ctx.scratch("memory_out", (n, s.hidden), ctx.dtype)
+        return linear(gated, self.wo, None, y, ctx.scratch)
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec:
+    hidden: int
+    num_heads: int  # value heads
+    qk_heads: int  # heads of q and k: head h reads q / k head h // (num_heads / qk_heads)
+    dim: int
+    vdim: int
+    taps: int  # of the convolutions on q, k and v; 1 keeps no state
+    decay_rank: int  # inner size of the two-step decay projection
+    gate_rank: int  # inner size of the two-step output-gate projection
+    eps: float
+    # checkpoint tensors (full names)
+    q_name: str
+    k_name: str
+    v_name: str
+    q_conv_name: str
+    k_conv_name: str
+    v_conv_name: str
+    beta_name: str  # [heads, hidden]
+    a_log_name: str  # [heads]
+    decay_in_name: str  # [decay_rank, hidden]
+    decay_out_name: str  # [heads * dim, decay_rank]
+    decay_bias_name: str  # [heads * dim]
+    gate_in_name: str  # [gate_rank, hidden]
+    gate_out_name: str  # [heads * vdim, gate_rank]
+    norm_name: str  # [vdim], shared by the heads
+    o_name: str
+    unit_eps: float = 1e-6  # q and k become x / sqrt(sum(x^2) + unit_eps) per head
+    kind: str = "channel_delta"
+
+
+@register_part("mixer", "channel_delta")
+class ChannelDelta(Mixer):
+    """The delta rule with a decay per head and key channel:
+
+        q, k, v <- silu(conv(h Wq^T)), ...;   q, k <- unit vectors per head;   q <- q dim^(-1/2)
+        beta = sigmoid(h Wb^T);   g = exp(-exp(A_log) softplus((h Wa1^T) Wa2^T + dt_bias))     [heads, dim]
+        S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q                   per head
+        out = (rms(o) * norm * sigmoid((h Wg1^T) Wg2^T)) Wo^T
+
+    One product gives ``[q | k | v | a1 | g1 | b]``; the convolution runs over the q, k and v columns;
+    the second steps of the decay and of the gate are products of their own (the decay's with a 32-bit
+    result); ``ems_delta_recurrence`` does the activation, the unit norms, beta, the decay and the rule
+    itself in 32 bits."""
+
+    win: torch.Tensor
+    wa2: torch.Tensor
+    wg2: torch.Tensor
+    dt_bias: torch.Tensor
+    a_log: torch.Tensor
+    norm: torch.Tensor
+    wo: torch.Tensor
+
+    def __init__(self, spec: ChannelDeltaSpec, prefix: str, shared=None) -> None:
+        super().__init__(spec, prefix, shared)
+        if spec.qk_heads <= 0 or spec.num_heads % spec.qk_heads:
+            raise ValueError(f"{spec.num_heads} heads over {spec.qk_heads} heads of q and k")
+        if spec.dim > 256:
+            raise ValueError(f"dim={spec.dim}: the memory kernel holds at most 256 rows per head")
+        self.qk, self.vv = spec.qk_heads * spec.dim, spec.num_heads * spec.vdim
+        self.conv_width = 2 * self.qk + self.vv
+        # every segment of the fused product begins at a multiple of 8 columns
+        self.a_at = _pad8(self.conv_width)
+        self.g_at = self.a_at + _pad8(spec.decay_rank)
+        self.b_at = self.g_at + _pad8(spec.gate_rank)
+        self.cols = self.b_at + _pad8(spec.num_heads)
+        q, kv = self.qk, 2 * self.qk
+        self.conv = build_part("conv", CausalTapsSpec(
+            self.conv_width, spec.taps, spec.q_conv_name, identity=False,
+            weight_parts=((spec.q_conv_name, 0, q), (spec.k_conv_name, q, kv), (spec.v_conv_name, kv, self.conv_width))),
+            prefix + ".conv", self.shared)
+        self._conv_state = self.conv.cache_need()
+        self._norm_rows: torch.Tensor | None = None
+
+    def children(self) -> dict[str, Part]:
+        return {"conv": self.conv}
+
+    def cache_need(self):
+        s: ChannelDeltaSpec = self.spec
+        state = FixedState((s.num_heads, s.dim * s.vdim), "float32")
+        return state if self._conv_state is None else (self._conv_state, state)
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        s: ChannelDeltaSpec = self.spec
+        qk, vv = self.qk, self.vv
+        return {
+            "win": ParamSpec((self.cols, s.hidden), [
+                Source(s.q_name, (0, qk)), Source(s.k_name, (qk, 2 * qk)), Source(s.v_name, (2 * qk, 2 * qk + vv)),
+                Source(s.decay_in_name, (self.a_at, self.a_at + s.decay_rank)),
+                Source(s.gate_in_name, (self.g_at, self.g_at + s.gate_rank)),
+                Source(s.beta_name, (self.b_at, self.b_at + s.num_heads))]),
+            "wa2": ParamSpec((s.num_heads * s.dim, s.decay_rank), [Source(s.decay_out_name)]),
+            "wg2": ParamSpec((vv, s.gate_rank), [Source(s.gate_out_name)]),
+            "dt_bias": ParamSpec((s.num_heads * s.dim,), [Source(s.decay_bias_name)], init="bias"),
+            "a_log": ParamSpec((s.num_heads,), [Source(s.a_log_name)], init="bias"),
+            "norm": ParamSpec((s.vdim,), [Source(s.norm_name)], init="ones"),
+            "wo": ParamSpec((s.hidden, vv), [Source(s.o_name)]),
+        }
+
+    def bind(self, params: dict[str, torch.Tensor]) -> None:
+        super().bind(params)
+        self._norm_rows = self.norm.repeat(self.spec.num_heads).contiguous()  # (the heads share one gain)
+
+    def streamed_params(self) -> list[str]:
+        return ["win", "wo"]
+
+    def scratch_elements_per_token(self) -> int:
+        s: ChannelDeltaSpec = self.spec
+        return self.cols + 2 * s.num_heads * s.dim + 5 * self.vv + s.hidden
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        s: ChannelDeltaSpec = self.spec
+        n, qk, vv, h = ctx.num_tokens, self.qk, self.vv, s.num_heads
+        conv_cache, state = (None, cache) if self._conv_state is None else cache
+        proj = ctx.scratch("delta_in", (n, self.cols), ctx.dtype)
+        linear(x, self.win, None, proj, ctx.scratch)
+        qkv = self.conv.forward(proj[:, :self.conv_width], ctx, conv_cache)
+        g_raw = ctx.scratch("delta_decay", (n, h * s.dim), torch.float32)
+        linear_f32_out(proj[:, self.a_at:self.a_at + s.decay_rank], self.wa2, g_raw)
+        gate = ctx.scratch("delta_gate", (n, vv), ctx.dtype)
+        linear(proj[:, self.g_at:self.g_at + s.gate_rank], self.wg2, None, gate, ctx.scratch)
+        read = ctx.scratch("memory_read", (n, vv), torch.float32)
+        K.delta_recurrence(qkv[:, :qk], qkv[:, qk:2 * qk], qkv[:, 2 * qk:], proj[:, self.b_at:self.b_at + h], g_raw,
+                           self.dt_bias, self.a_log, h, s.qk_heads, s.dim, s.vdim, state.state, state.slots,
+                           ctx.cu_q, ctx.num_rows, read, act="silu", unit_eps=s.unit_eps, q_scale=s.dim ** -0.5)
+        gated = ctx.scratch("memory_gated", (n, vv), ctx.dtype)
+        K.group_norm_gate(read, h, s.eps, self._norm_rows, gate, gated)
+        y = ctx.scratch("memory_out", (n, s.hidden), ctx.dtype)
+        return linear(gated, self.wo, None, y, ctx.scratch)

@@ -14,6 +14,13 @@
   `v_head_dim` numbers) before they are cached; each head's sum over the values is then turned back by
   the query's position, so that the output depends on distances only.
 
+* a short causal convolution over time on every channel of q, k and v right behind the projections
+  (`conv_taps`; the last taps - 1 projected rows of a request are state of the mixer);
+* gains on the normed q and k (`q_norm_name`, `k_norm_name`: [head_dim], shared by the heads), and the
+  norm BEFORE the rotation instead of behind it (`norm_before_rotation`);
+* capped scores: a scaled score s enters the softmax as ``softcap * tanh(s / softcap)``;
+* a bias on the output projection.
+
 ``[q | k | (v) | gate] = x W^T + b`` is one product; one kernel rotates, norms and writes the
 cache; the attention kernel applies mask, sink and gate; then ``o = attn Wo^T``.  Scores, softmax,
 rotation and the unit norms are 32-bit.  With a chunk mask the cache gives back the pages of
@@ -29,8 +36,9 @@ import torch
 
 from emberserve_b200 import kernels as K
 from emberserve_b200.parts.attention import decode_splits
-from emberserve_b200.parts.base import (Mixer, PagedKV, PagedKVHandle, ParamSpec, Source, StepContext,
-                                        register_part)
+from emberserve_b200.parts.base import (Mixer, PagedKV, PagedKVHandle, ParamSpec, Part, Source, StepContext,
+                                        build_part, register_part)
+from emberserve_b200.parts.conv import CausalTapsSpec
 from emberserve_b200.parts.linear import linear
 
 
@@ -60,6 +68,15 @@ class SinkAttentionSpec:
     v_head_dim: int | None = None  # numbers per value head (None: head_dim)
     v_norm_eps: float | None = None  # unit RMS of every value head
     value_position: Any = None  # rotary spec over v_head_dim numbers: values turned when cached, the sum turned back
+    conv_taps: int = 1  # > 1: a causal convolution of that many taps on q, k and v
+    q_conv_name: str | None = None  # checkpoint tensors [channels, taps]
+    k_conv_name: str | None = None
+    v_conv_name: str | None = None
+    q_norm_name: str | None = None  # [head_dim] gains of the normed q and k (with qk_norm_eps)
+    k_norm_name: str | None = None
+    norm_before_rotation: bool = False
+    softcap: float | None = None
+    o_bias_name: str | None = None
 
 
 @register_part("mixer", "sink_attention")
@@ -68,6 +85,9 @@ class SinkAttention(Mixer):
     wo: torch.Tensor
     bqkv: torch.Tensor | None = None
     sink: torch.Tensor | None = None
+    bo: torch.Tensor | None = None
+    q_gain: torch.Tensor | None = None
+    k_gain: torch.Tensor | None = None
 
     def __init__(self, spec: SinkAttentionSpec, prefix: str, shared=None) -> None:
         super().__init__(spec, prefix, shared)
@@ -95,11 +115,28 @@ class SinkAttention(Mixer):
         if self.value_position is not None and self.value_position.spec.rotary_dim != self.v_dim:
             raise ValueError("the rotation of the values covers the whole value head")
         self._sink32: torch.Tensor | None = None
+        if (spec.q_norm_name is None) != (spec.k_norm_name is None) or (
+                spec.q_norm_name is not None and spec.qk_norm_eps is None):
+            raise ValueError("gains on q and k come in pairs and need qk_norm_eps")
+        self.conv = None
+        if spec.conv_taps > 1 or spec.q_conv_name is not None:
+            if spec.v_name is None or None in (spec.q_conv_name, spec.k_conv_name, spec.v_conv_name):
+                raise ValueError("the convolution filters projected q, k and v and needs a weight for each")
+            q, kv = self.q_size, self.kv_size
+            self.conv = build_part("conv", CausalTapsSpec(
+                self.gate_at, spec.conv_taps, spec.q_conv_name, identity=False,
+                weight_parts=((spec.q_conv_name, 0, q), (spec.k_conv_name, q, q + kv),
+                              (spec.v_conv_name, q + kv, self.gate_at))), prefix + ".conv", self.shared)
+        self._conv_state = self.conv.cache_need() if self.conv is not None else None
 
-    def cache_need(self) -> PagedKV:
+    def children(self) -> dict[str, Part]:
+        return {} if self.conv is None else {"conv": self.conv}
+
+    def cache_need(self):
         s: SinkAttentionSpec = self.spec
-        return PagedKV(s.num_kv_heads, s.head_dim, s.window, s.chunk, keep_first=int(s.keep_first or 0),
-                       v_head_dim=None if self.v_dim == s.head_dim else self.v_dim)
+        pages = PagedKV(s.num_kv_heads, s.head_dim, s.window, s.chunk, keep_first=int(s.keep_first or 0),
+                        v_head_dim=None if self.v_dim == s.head_dim else self.v_dim)
+        return pages if self._conv_state is None else (pages, self._conv_state)
 
     def param_specs(self) -> dict[str, ParamSpec]:
         s: SinkAttentionSpec = self.spec
@@ -119,6 +156,11 @@ class SinkAttention(Mixer):
             specs["bqkv"] = ParamSpec((self.cols,), [Source(b, r) for b, r in biased], init="bias")
         if s.sink_name is not None:
             specs["sink"] = ParamSpec((s.num_heads,), [Source(s.sink_name)], init="bias")
+        if s.o_bias_name is not None:
+            specs["bo"] = ParamSpec((s.hidden,), [Source(s.o_bias_name)], init="bias")
+        if s.q_norm_name is not None:
+            specs["q_gain"] = ParamSpec((s.head_dim,), [Source(s.q_norm_name)], init="ones")
+            specs["k_gain"] = ParamSpec((s.head_dim,), [Source(s.k_norm_name)], init="ones")
         return specs
 
     def bind(self, params: dict[str, torch.Tensor]) -> None:
@@ -129,13 +171,19 @@ class SinkAttention(Mixer):
         return ["wqkv", "wo"]
 
     def scratch_elements_per_token(self) -> int:
-        return self.cols + self.o_size + self.spec.hidden
+        return self.cols + self.o_size + self.spec.hidden  # (a convolution's output is its own part's)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVHandle) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         s: SinkAttentionSpec = self.spec
         n, b = ctx.num_tokens, ctx.num_rows
+        conv_cache = None
+        if self._conv_state is not None:
+            cache, conv_cache = cache
         proj = ctx.scratch("sink_qkv", (n, self.cols), ctx.dtype)
         linear(x, self.wqkv, self.bqkv, proj, ctx.scratch)
+        gate = proj[:, self.gate_at:self.gate_at + self.gate_cols] if self.gate_cols else None
+        if self.conv is not None:  # (the gate's columns, if any, stay where they are)
+            proj = self.conv.forward(proj[:, :self.gate_at], ctx, conv_cache)
         table, rot, pairing = None, 0, "half"
         if self.position is not None:
             r = self.position.rotary(ctx.device)
@@ -146,11 +194,11 @@ class SinkAttention(Mixer):
             vtable, vpairing = self.value_position.rotary(ctx.device)[0], self.value_position.pairing
         K.qk_prep(proj, s.num_heads, s.num_kv_heads, s.head_dim, ctx.positions, ctx.row_of_token, table, rot,
                   pairing, s.qk_norm_eps, cache.k, cache.v, cache.block_tables, s.v_name is None, cache.write,
-                  v_norm_eps=s.v_norm_eps, v_table=vtable, v_pairing=vpairing)
+                  v_norm_eps=s.v_norm_eps, v_table=vtable, v_pairing=vpairing, q_gain=self.q_gain,
+                  k_gain=self.k_gain, norm_first=s.norm_before_rotation)
         out = ctx.scratch("attn_out", (n, self.o_size), ctx.dtype)
         extras = dict(keep_first=int(s.keep_first or 0), out_table=vtable, out_pairing=vpairing,
-                      positions=ctx.positions if vtable is not None else None)
-        gate = proj[:, self.gate_at:self.gate_at + self.gate_cols] if self.gate_cols else None
+                      positions=ctx.positions if vtable is not None else None, softcap=s.softcap)
         kern = ctx.extra.get("attn_kernel", "auto")
         if ctx.all_decode and n == b:
             # one token per row: the keys of a row are split over blocks when rows are few.  A chunk
@@ -173,4 +221,4 @@ class SinkAttention(Mixer):
                                      window=s.window, chunk=s.chunk, sinks=self._sink32, gate=gate, kernel=kern,
                                      **extras)
         y = ctx.scratch("mixer_out", (n, s.hidden), ctx.dtype)
-        return linear(out, self.wo, None, y, ctx.scratch)
+        return linear(out, self.wo, self.bo, y, ctx.scratch)

@@ -64,7 +64,17 @@ def resolve_architecture(cfg: dict[str, Any]) -> Architecture:
 
 def load_config(model_dir: str | os.PathLike) -> ModelConfig:
     cfg = read_config_json(model_dir)
-    return resolve_architecture(cfg).config_cls.from_dict(cfg)
+    config = resolve_architecture(cfg).config_cls.from_dict(cfg)
+    if config.wants_tensor_shapes:
+        from emberserve_b200.weights.safetensors_io import open_model_files
+        try:
+            files = open_model_files(model_dir)
+        except FileNotFoundError:
+            files = []
+        shapes = {name: tuple(info.shape) for f in files for name, info in f.tensors.items()}
+        if shapes:
+            config = config.with_tensor_shapes(shapes)
+    return config
 
 
 def architecture_of(config: ModelConfig) -> Architecture:

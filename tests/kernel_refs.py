@@ -404,18 +404,19 @@ def moe_max_tiles(num_pairs, num_experts, tile_rows):
 
 
 def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_tiles, align=1, big=None, inv=None,
-              scoring="softmax"):
+              scoring="softmax", correction=None, renorm_eps=0.0, scale=1.0, plan_experts=None):
     assert align == 1, "the aligned layout belongs to the GPU path"
     n, e = logits.shape
     s = torch.sigmoid(logits.float()) if scoring == "sigmoid" else torch.softmax(logits.float(), -1)
     chosen = torch.zeros(n, top, dtype=torch.long)
-    z = logits.clone()
+    z = logits.clone() if correction is None else s + correction.float()
     for k in range(top):
         chosen[:, k] = torch.argmax(z, -1)  # the first of equal maxima
         z[torch.arange(n), chosen[:, k]] = float("-inf")
     w = torch.gather(s, 1, chosen)
     if renormalize:
-        w = w / w.sum(-1, keepdim=True)
+        w = w / (w.sum(-1, keepdim=True) + renorm_eps)
+    w = w * scale
     ids.view(-1)[:n * top] = chosen.reshape(-1).to(torch.int32)
     weights.view(-1)[:n * top] = w.reshape(-1)
     flat = chosen.reshape(-1)
@@ -427,10 +428,24 @@ def moe_route(logits, top, renormalize, ids, weights, offsets, perm, plan, max_t
 
 
 def moe_up(x, wgu, perm, offsets, plan, max_tiles, top, act, out, kernel="auto", in_scale=None, limit=0.0,
-           alpha=1.0):
+           alpha=1.0, gated=True):
     e, ff2, k = wgu.shape
     ff = ff2 // 2
     off = offsets.tolist()
+    if not gated:  # experts without a gate: act(x Wu^T) of the rounded sum
+        for ex in range(e):
+            lo, hi = off[ex], off[ex + 1]
+            if hi > lo:
+                y = x[(perm[lo:hi] // top).long()].float() @ wgu[ex].float().t()
+                if in_scale is not None:
+                    y = y * in_scale[perm[lo:hi].long()][:, None]
+                y = y.to(out.dtype).float()
+                if act == "gelu":
+                    y = 0.5 * y * (1 + torch.erf(y / math.sqrt(2.0)))
+                else:
+                    y = _glu_activation(y, act)
+                out[lo:hi] = y.to(out.dtype)
+        return
     for ex in range(e):
         lo, hi = off[ex], off[ex + 1]
         if hi <= lo:
@@ -454,9 +469,12 @@ def moe_down(act, wdown, perm, offsets, plan, max_tiles, y, kernel="auto"):
         y[perm[lo:hi].long()] = (act[lo:hi].float() @ wdown[ex].float().t()).to(act.dtype).float()
 
 
-def moe_combine(y, weights, out, top, extra=None):
+def moe_combine(y, weights, out, top, extra=None, ids=None, x=None, num_real=0):
     n, h = out.shape
     rows = y[:n * top].view(n, top, h)
+    if x is not None:  # an expert at or past num_real returns its input
+        same = ids.view(-1)[:n * top].view(n, top) >= num_real
+        rows = torch.where(same[:, :, None], x.float()[:, None, :], rows)
     if weights is not None:
         rows = rows * weights.view(-1)[:n * top].view(n, top, 1)
     total = rows.sum(1)
@@ -473,6 +491,8 @@ def unary_act(x, out, act):
         y = torch.relu(z) ** 2
     elif act == "gelu_tanh":
         y = 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+    elif act == "gelu":
+        y = 0.5 * z * (1 + torch.erf(z / math.sqrt(2.0)))
     else:
         y = z / (1 + torch.exp(-z))
     out.copy_(y.to(out.dtype))
@@ -480,7 +500,7 @@ def unary_act(x, out, act):
 
 def qk_prep(proj, num_heads, num_kv_heads, head_dim, positions, row_of_token, table, rot_dims, pairing, norm_eps,
             kcache, vcache, block_tables, values_are_keys, write=True, v_norm_eps=None, v_table=None,
-            v_pairing="half"):
+            v_pairing="half", q_gain=None, k_gain=None, norm_first=False):
     n, d, dv = proj.shape[0], head_dim, vcache.shape[3]
     nq, nk = num_heads * d, num_kv_heads * d
     pos = positions[:n].long()
@@ -488,12 +508,20 @@ def qk_prep(proj, num_heads, num_kv_heads, head_dim, positions, row_of_token, ta
     k_raw = proj[:, nq:nq + nk]
     k = k_raw.float().view(n, num_kv_heads, d)
     v = k_raw if values_are_keys else proj[:, nq + nk:nq + nk + num_kv_heads * dv]
+    def normed(q, k):
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + norm_eps)
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + norm_eps)
+        if q_gain is not None:
+            q, k = q * q_gain.float(), k * k_gain.float()
+        return q, k
+
+    if norm_eps is not None and norm_first:
+        q, k = normed(q, k)
     if table is not None and rot_dims:
         cs = table[pos][:, None]
         q, k = _rotate_pairs(q, cs, rot_dims, pairing), _rotate_pairs(k, cs, rot_dims, pairing)
-    if norm_eps is not None:
-        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + norm_eps)
-        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + norm_eps)
+    if norm_eps is not None and not norm_first:
+        q, k = normed(q, k)
     vv = v.reshape(n, num_kv_heads, dv).clone()
     if v_norm_eps is not None or v_table is not None:
         vf = vv.float()
@@ -514,7 +542,7 @@ def qk_prep(proj, num_heads, num_kv_heads, head_dim, positions, row_of_token, ta
 def paged_attention_masked(q, out, kcache, vcache, block_tables, cu_q, starts, num_rows, num_tokens, num_heads,
                            num_kv_heads, head_dim, scale, max_q_len, window=None, chunk=None, sinks=None, gate=None,
                            splits=1, scratch=None, kernel="auto", keep_first=0, out_table=None, out_pairing="half",
-                           positions=None):
+                           positions=None, softcap=None):
     page_size = kcache.shape[2]
     dv = vcache.shape[3]
     groups = num_heads // num_kv_heads
@@ -536,6 +564,8 @@ def paged_attention_masked(q, out, kcache, vcache, block_tables, cu_q, starts, n
         v = vcache[pages, :, keys % page_size, :].float().repeat_interleave(groups, dim=1).permute(1, 0, 2)
         qq = q[q0:q1, : num_heads * head_dim].float().view(qlen, num_heads, head_dim).permute(1, 0, 2)
         scores = torch.matmul(qq, k.transpose(-1, -2)) * scale  # [H, qlen, T]
+        if softcap:
+            scores = softcap * torch.tanh(scores / softcap)
         qpos = torch.arange(st[b], ctx)[:, None]
         hidden = torch.zeros(qlen, keys.numel(), dtype=torch.bool)
         if window:
@@ -573,10 +603,11 @@ def _memory_act(z, act):
 
 
 def matrix_recurrence(q, k, v, num_heads, dim, vdim, state, slots, cu_q, num_rows, out, act="none", q_scale=1.0,
-                      decay_head=None, a=None, b=None, denom_floor=None, denom=None, denom_eps=0.0):
+                      decay_head=None, a=None, b=None, denom_floor=None, denom=None, denom_eps=0.0, qk_heads=None):
     n, H, D, V = q.shape[0], num_heads, dim, vdim
-    qq = _memory_act(q[:, :H * D].float(), act).view(n, H, D) * q_scale
-    kk = _memory_act(k[:, :H * D].float(), act).view(n, H, D)
+    G = qk_heads or H
+    qq = (_memory_act(q[:, :G * D].float(), act).view(n, G, D) * q_scale).repeat_interleave(H // G, dim=1)
+    kk = _memory_act(k[:, :G * D].float(), act).view(n, G, D).repeat_interleave(H // G, dim=1)
     vv = _memory_act(v[:, :H * V].float(), act).view(n, H, V)
     cu = cu_q.tolist()
     for r in range(num_rows):
@@ -646,13 +677,76 @@ def rglru_scan(u, pre, bias_r, bias_i, lam, y, y_act, cmul, state, slots, cu_q, 
         state[slot] = S
 
 
+def add_scaled_norm2(deltas, residual, gain1, gain2, gain_offset, eps, out1, out2):
+    for d, sc in deltas:
+        residual += sc * d.float()
+    x = residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps)
+    if out1 is not None:
+        out1.copy_((x * (gain1.float() + gain_offset)).to(out1.dtype))
+    if out2 is not None:
+        out2.copy_((x * (gain2.float() + gain_offset)).to(out2.dtype))
+
+
+def stream_norm(residual, gain, gain_offset, eps):
+    residual.copy_(residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps) * (gain.float() + gain_offset))
+
+
+def softcap(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+
+
+def delta_recurrence(q, k, v, beta, g_raw, g_bias, a_log, num_heads, qk_heads, dim, vdim, state, slots, cu_q,
+                     num_rows, out, act="silu", unit_eps=1e-6, q_scale=1.0):
+    n, H, G, D, V = q.shape[0], num_heads, qk_heads, dim, vdim
+    qq = _memory_act(q[:, :G * D].float(), act).view(n, G, D)
+    kk = _memory_act(k[:, :G * D].float(), act).view(n, G, D)
+    if unit_eps is not None:
+        qq = qq * torch.rsqrt(qq.pow(2).sum(-1, keepdim=True) + unit_eps)
+        kk = kk * torch.rsqrt(kk.pow(2).sum(-1, keepdim=True) + unit_eps)
+    qq = (qq * q_scale).repeat_interleave(H // G, dim=1)
+    kk = kk.repeat_interleave(H // G, dim=1)
+    vv = _memory_act(v[:, :H * V].float(), act).view(n, H, V)
+    bb = torch.sigmoid(beta[:, :H].float())
+    gg = torch.exp(-torch.exp(a_log.float())[None, :, None]
+                   * torch.nn.functional.softplus(g_raw + g_bias.float().reshape(-1)).view(n, H, D))
+    cu = cu_q.tolist()
+    for r in range(num_rows):
+        slot = int(slots[r])
+        S = state[slot].reshape(H, D, V).clone()
+        for t in range(cu[r], cu[r + 1]):
+            S = gg[t][:, :, None] * S
+            u = bb[t][:, None] * (vv[t] - torch.einsum("hdv,hd->hv", S, kk[t]))
+            S = S + kk[t][:, :, None] * u[:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, qq[t]).reshape(-1)
+        state[slot] = S.reshape(H, D * V)
+
+
+def ssm_gates(x, bias, a_log, a, b):
+    dt = torch.nn.functional.softplus(x.float() + bias.float())
+    a.copy_(torch.exp(-torch.exp(a_log.float()) * dt))
+    b.copy_(dt)
+
+
+def gate_group_norm(o, groups, eps, weight, out, z=None, skip=None, x=None, x_act="none", head_width=None):
+    n, c = o.shape
+    y = o
+    if skip is not None:
+        y = y + skip.float().repeat_interleave(head_width or c) * _memory_act(x[:, :c].float(), x_act)
+    if z is not None:
+        zz = z[:, :c].float()
+        y = y * zz * torch.sigmoid(zz)
+    y = y.view(n, groups, c // groups)
+    y = (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, c) * weight.float()
+    out.copy_(y.to(out.dtype))
+
+
 ALL = ["gemm_smallm", "gemm_smallm_gated", "check_status", "embedding", "add_rmsnorm", "silu_mul", "rope_table", "rope_kv_write",
        "attention_scratch_bytes", "paged_attention", "argmax", "repetition_penalty", "sample",
        "stream_inject", "add_norm_grouped", "glu_act", "causal_taps", "latent_prep", "rope_inplace",
        "latent_attention_scratch_bytes", "latent_attention", "heads_gate", "moe_tile_rows", "moe_max_tiles",
        "moe_route", "moe_up", "moe_down", "moe_combine", "unary_act", "qk_prep", "paged_attention_masked",
        "norm_mean2", "matrix_recurrence", "mlstm_gates", "group_norm_gate", "rglru_scan", "add_cast", "token_gate",
-       "depth_mix"]
+       "depth_mix", "add_scaled_norm2", "stream_norm", "softcap", "delta_recurrence", "ssm_gates", "gate_group_norm"]
 
 
 def install(monkeypatch) -> None:
