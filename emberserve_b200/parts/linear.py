@@ -127,6 +127,12 @@ def _norm_before(x: ScaledRows) -> K.NormBefore:
     return K.NormBefore(x.sumsq, x.parts, x.x.shape[1], x.eps)
 
 
+def _gated_twin(weight: torch.Tensor) -> "torch.Tensor | None":
+    """The tiled copy of a [gate; up] weight for the weight-streaming kernel, which reads a tile of 128 gate
+    rows and the tile of up rows beside it: only where the up rows begin at a tile's edge."""
+    return tiled_twin(weight) if (weight.shape[0] // 2) % 128 == 0 else None
+
+
 def gated_linear(x: "torch.Tensor | ScaledRows", weight: torch.Tensor, out: torch.Tensor) -> bool:
     """out = silu(x Wg^T) * (x Wu^T) with weight = [Wg; Wu], in one kernel, where a hand-written
     kernel takes the case: the weight-streaming one up to 64 rows, the two-SM one (256 x 256
@@ -138,11 +144,11 @@ def gated_linear(x: "torch.Tensor | ScaledRows", weight: torch.Tensor, out: torc
     (9.7 us against 11.9): inside a graph one launch less weighs more than the kernel's fixed cost."""
     if isinstance(x, ScaledRows):  # a norm that this product has to finish
         if _use_smallm(x.x, weight, None, out, K.GEMM_NORM_ROWS):
-            K.gemm_smallm_gated(x.x, weight, out, norm_before=_norm_before(x), twin=tiled_twin(weight))
+            K.gemm_smallm_gated(x.x, weight, out, norm_before=_norm_before(x), twin=_gated_twin(weight))
             return True
         x = x.materialize()
     if _use_smallm(x, weight, None, out, _GATED_ROWS):
-        K.gemm_smallm_gated(x, weight, out, twin=tiled_twin(weight))
+        K.gemm_smallm_gated(x, weight, out, twin=_gated_twin(weight))
         return True
     if _use_smallm(x, weight, None, out, 1 << 30) and K.gemm_large_gated_supported(
             x.shape[0], out.shape[1], x.shape[1]):
