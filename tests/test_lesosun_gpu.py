@@ -1,0 +1,573 @@
+"""Lesosun on the GPU: every new kernel and kernel option alone against its restatement and against
+the plain implementation (``plain_lesosun``), keys that one score singles out at the first position, at
+page borders, far back, at the query itself and one past it, under capped scores; memories whose
+slots change hands; the engine under every way of cutting the same requests, batches against each
+request alone, long decoding, other sizes, and greedy generation through the entry point and its
+scheduler."""
+
+from __future__ import annotations
+
+import json
+import math
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs as R
+import plain_lesosun as plain
+import replay_cases as rc
+import tiny_lesosun as tl
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+DEV = "cuda:0"
+LENGTHS = {"les_a": [1, 2, 9, 23, 40, 31, 130], "les_b": [3, 17, 50, 8, 70, 33, 150],
+           "les_c": [2, 48, 11, 61, 35, 5, 97]}
+TOL32 = 5e-5  # of the largest |logit|
+TOL16 = 6e-2  # bfloat16 against the 64-bit plain implementation, weights drawn wide
+DTYPES = pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+
+
+def _i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+def _K():
+    from emberserve_b200 import kernels
+
+    return kernels
+
+
+def _close(got, want, dtype, what="", tol=None):
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    scale = float(want.abs().max()) + 1e-30
+    tol = tol if tol is not None else (2e-5 if dtype == torch.float32 else 1.2e-2)
+    err = float((got - want).abs().max()) / scale
+    assert err <= tol, f"{what}: {err:.3e} of scale {scale:.3e}"
+
+
+@pytest.fixture(scope="module")
+def les_dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("lesosun")
+    return {name: tl.write_model(cfg, root / name, tl.SEEDS[name]) for name, cfg in tl.ALL.items()}
+
+
+# ---- kernels alone ----------------------------------------------------------------------------
+
+@DTYPES
+@pytest.mark.parametrize("c", [40, 250, 2048, 5000])
+def test_sum_into_the_stream_and_two_norms_of_it(dtype, c):
+    g = torch.Generator().manual_seed(c)
+    n = 7
+    res = torch.randn(n, c, generator=g) * 3
+    deltas = [((torch.randn(n, c, generator=g)).to(dtype), s) for s in (0.5, -1.25, 2.0)]
+    g1, g2 = (0.3 * torch.randn(c, generator=g)).to(dtype), (0.3 * torch.randn(c, generator=g)).to(dtype)
+    for count, two in ((3, True), (1, True), (0, False), (2, False)):
+        want_res = res.clone()
+        w1, w2 = torch.zeros(n, c, dtype=dtype), torch.zeros(n, c, dtype=dtype)
+        R.add_scaled_norm2(deltas[:count], want_res, g1, g2 if two else None, 1.0, 1e-5, w1, w2 if two else None)
+        got_res = res.clone().to(DEV)
+        o1, o2 = torch.zeros(n, c, dtype=dtype, device=DEV), torch.zeros(n, c, dtype=dtype, device=DEV)
+        _K().add_scaled_norm2([(d.to(DEV), s) for d, s in deltas[:count]], got_res, g1.to(DEV),
+                              g2.to(DEV) if two else None, 1.0, 1e-5, o1, o2 if two else None)
+        _close(got_res, want_res, torch.float32, "stream")
+        _close(o1, w1, dtype, "first norm")
+        if two:
+            _close(o2, w2, dtype, "second norm")
+        # the plain norm with a gain stored minus one
+        _close(o1, plain.rms(want_res.double(), 1e-5) * (1 + g1.double()), dtype, "against the plain norm")
+    # the sum alone (no output): what a final norm asks for first
+    got_res = res.clone().to(DEV)
+    _K().add_scaled_norm2([(d.to(DEV), s) for d, s in deltas], got_res, None, None, 0.0, 1e-5, None, None)
+    _close(got_res, res + sum(s * d.float() for d, s in deltas), torch.float32, "sum alone")
+    # the stream normed in place, and capped values
+    x = res.clone().to(DEV)
+    _K().stream_norm(x, g1.to(DEV), 1.0, 1e-5)
+    _close(x, plain.rms(res.double(), 1e-5) * (1 + g1.double()), torch.float32, "stream norm")
+    y = (res * 9).to(DEV)
+    _K().softcap(y, 7.5)
+    _close(y, 7.5 * torch.tanh(res.double() * 9 / 7.5), torch.float32, "cap")
+
+
+@DTYPES
+@pytest.mark.parametrize("act", ["gelu", "silu"])
+def test_erf_gelu(dtype, act):
+    g = torch.Generator().manual_seed(1)
+    x = (3 * torch.randn(33, 50, generator=g)).to(dtype)
+    out = torch.zeros_like(x, device=DEV)
+    _K().unary_act(x.to(DEV), out, act)
+    want = plain.gelu_erf(x.double()) if act == "gelu" else plain.silu(x.double())
+    _close(out, want, dtype, act)
+
+
+def _paged(g, dtype, nkv, d, dv, page_size, ctx_lens):
+    """Block tables over shuffled pages for requests of the given lengths; stale contents everywhere."""
+    pages_per = [-(-c // page_size) for c in ctx_lens]
+    total = sum(pages_per) + 3
+    perm = torch.randperm(total, generator=g).tolist()
+    bt = torch.zeros(len(ctx_lens), max(pages_per), dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(pages_per):
+        bt[b, :n] = torch.tensor(perm[at:at + n], dtype=torch.int32)
+        at += n
+    kc = torch.randn(total, nkv, page_size, d, generator=g).to(dtype)
+    vc = torch.randn(total, nkv, page_size, dv, generator=g).to(dtype)
+    return bt, kc, vc
+
+
+@DTYPES
+@pytest.mark.parametrize("rot,d,dv,first", [(4, 8, 16, True), (16, 16, 16, True), (6, 24, 8, False), (0, 40, 40, True),
+                                            (64, 128, 128, True)])
+def test_norm_with_gains_before_the_rotation_and_cache_write(dtype, rot, d, dv, first):
+    g = torch.Generator().manual_seed(rot + d)
+    nh, nkv, ps = 6, 2, 4
+    starts, qlens = [0, 9, 3], [7, 1, 5]
+    bt, kc, vc = _paged(g, dtype, nkv, d, dv, ps, [s + q for s, q in zip(starts, qlens)])
+    n = sum(qlens)
+    proj = torch.randn(n, (nh + nkv) * d + nkv * dv + 8, generator=g).to(dtype)
+    pos = _i32(np.concatenate([np.arange(s, s + q) for s, q in zip(starts, qlens)]))
+    row_of = _i32(np.repeat(np.arange(3), qlens))
+    qg, kg = (1 + 0.4 * torch.randn(d, generator=g)).to(dtype), (1 + 0.4 * torch.randn(d, generator=g)).to(dtype)
+    table = None
+    if rot:
+        inv = (50.0 ** (-torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+        table = R.rope_table(inv, 32)
+    want = (proj.clone(), kc.clone(), vc.clone())
+    R.qk_prep(want[0], nh, nkv, d, pos.cpu(), row_of.cpu(), table, rot, "interleaved", 1e-5, want[1], want[2], bt, False,
+              q_gain=qg, k_gain=kg, norm_first=first)
+    got = (proj.to(DEV), kc.to(DEV), vc.to(DEV))
+    _K().qk_prep(got[0], nh, nkv, d, pos, row_of, None if table is None else table.to(DEV), rot, "interleaved", 1e-5,
+                 got[1], got[2], bt.to(DEV), False, q_gain=qg.to(DEV), k_gain=kg.to(DEV), norm_first=first)
+    for a, b, what in zip(got, want, ("q", "k cache", "v cache")):
+        _close(a, b, dtype, what)
+    if first and rot:  # the plain implementation's order: norm, gain, then rotation
+        t = 5  # a token of request 0, position 5
+        x = proj[t, :d].double()[None, None, :].repeat(6, 1, 1)
+        turned = plain.rotate_interleaved(plain.rms(x, 1e-5) * qg.double(), rot, 50.0)[5, 0]
+        _close(got[0][t, :d], turned, dtype, "against the plain order")
+        page, slot = int(bt[0, 5 // ps]), 5 % ps
+        assert torch.equal(got[2][page, 0, slot].cpu(), proj[t, (nh + nkv) * d:(nh + nkv) * d + dv])
+
+
+def _attention_case(g, dtype, nh, nkv, d, dv, ps, starts, qlens):
+    ctx = [s + q for s, q in zip(starts, qlens)]
+    bt, kc, vc = _paged(g, dtype, nkv, d, dv, ps, ctx)
+    n = sum(qlens)
+    q = torch.randn(n, nh * d + 16, generator=g).to(dtype)
+    cu = _i32(np.concatenate([[0], np.cumsum(qlens)]))
+    return q, bt, kc, vc, cu, _i32(starts), n
+
+
+def _run_attention(case, nh, nkv, d, dv, scale, max_q, rows, cap, splits=1, dev=True, kernel="auto"):
+    q, bt, kc, vc, cu, st, n = case
+    mod = _K() if dev else R
+    mv = (lambda t: t.to(DEV)) if dev else (lambda t: t.cpu())
+    out = torch.zeros(n, nh * dv, dtype=q.dtype, device=DEV if dev else "cpu")
+    scratch = None
+    if splits > 1 and dev:
+        scratch = torch.empty(mod.attention_scratch_bytes(n, nh, dv, splits) // 4, dtype=torch.float32, device=DEV)
+    mod.paged_attention_masked(mv(q), out, mv(kc), mv(vc), mv(bt), mv(cu), mv(st), rows, n, nh, nkv, d, scale, max_q,
+                               splits=splits, scratch=scratch, softcap=cap, kernel=kernel)
+    return out
+
+
+@DTYPES
+@pytest.mark.parametrize("nh,nkv,d,dv,ps,cap", [(6, 2, 8, 16, 4, 2.0), (4, 4, 16, 16, 16, 5.0), (5, 1, 40, 8, 8, 1.5),
+                                                (8, 8, 64, 64, 16, 3.0), (3, 3, 128, 128, 32, 4.0),
+                                                (4, 2, 128, 256, 16, 6.0), (2, 1, 24, 24, 16, None)])
+def test_capped_attention_against_dense(dtype, nh, nkv, d, dv, ps, cap):
+    g = torch.Generator().manual_seed(nh * d)
+    starts, qlens = [0, 61, 17, 130, 5], [33, 1, 20, 1, 2]  # prompts, portions and single tokens in one step
+    case = _attention_case(g, dtype, nh, nkv, d, dv, ps, starts, qlens)
+    want = _run_attention(case, nh, nkv, d, dv, 0.9, max(qlens), 5, cap, dev=False)
+    for kernel in ("auto", "generic"):
+        _close(_run_attention(case, nh, nkv, d, dv, 0.9, max(qlens), 5, cap, kernel=kernel), want, dtype, kernel)
+    if cap:  # the cap matters at these scores
+        free = _run_attention(case, nh, nkv, d, dv, 0.9, max(qlens), 5, None, dev=False)
+        assert float((free.float() - want.float()).abs().max()) > 0.05
+    # single tokens only, keys split over blocks and merged
+    starts, qlens = [200, 7, 64, 0], [1, 1, 1, 1]
+    case = _attention_case(g, dtype, nh, nkv, d, dv, ps, starts, qlens)
+    want = _run_attention(case, nh, nkv, d, dv, 0.9, 1, 4, cap, dev=False)
+    for splits in (1, 2, 5):
+        _close(_run_attention(case, nh, nkv, d, dv, 0.9, 1, 4, cap, splits=splits), want, dtype, f"splits={splits}")
+
+
+@DTYPES
+@pytest.mark.parametrize("d,dv", [(16, 24), (128, 128), (128, 256)], ids=["generic", "tensor-core-size", "wide-values"])
+@pytest.mark.parametrize("decode", [False, True], ids=["prompt", "decoded"])
+def test_a_planted_key_shows_under_the_cap(dtype, decode, d, dv):
+    """One key is made to win the softmax (its capped score stands at the cap, every other near zero) and
+    its value is a one-hot: the output shows whether the query saw it.  Pages of 16: the first key of the
+    sequence, keys far back among hundreds, the first and last key of a page, the query itself are seen;
+    the key one past the query (in a prompt) is not."""
+    nh, nkv, ps, cap = 2, 1, 16, 12.0
+    g = torch.Generator().manual_seed(5)
+    qpos = 300
+    for key, seen in ((0, True), (1, True), (15, True), (16, True), (137, True), (287, True), (288, True), (299, True),
+                      (300, True), (301, False), (303, False)):
+        if decode and key > qpos:
+            continue
+        start, qlen = (qpos, 1) if decode else (qpos - 9, 14)
+        case = list(_attention_case(g, dtype, nh, nkv, d, dv, ps, [start], [qlen]))
+        q, bt, kc, vc = case[0], case[1], case[2].float() * 0.05, case[3].float() * 0.1
+        row = qpos - start
+        q[row, :nh * d] = 0
+        q[row, :d] = 4.0
+        q[row, d:2 * d] = 4.0
+        page, slot = int(bt[0, key // ps]), key % ps
+        kc[page, 0, slot] = 4.0
+        vc[page, 0, slot] = 0
+        vc[page, 0, slot, 3] = 50.0
+        case[2], case[3] = kc.to(dtype), vc.to(dtype)
+        out = _run_attention(case, nh, nkv, d, dv, 4.0 / d, qlen, 1, cap)
+        got = float(out[row, 3])
+        assert (got > 40.0) == seen, f"key {key} from position {qpos}: {got}"
+        want = _run_attention(case, nh, nkv, d, dv, 4.0 / d, qlen, 1, cap, dev=False)
+        _close(out, want, dtype, f"key {key}")
+
+
+@pytest.mark.parametrize("h,g_,d,v", [(4, 2, 5, 6), (3, 1, 8, 8), (6, 3, 16, 4), (2, 2, 33, 70), (8, 2, 128, 64),
+                                       (1, 1, 200, 24)])
+@DTYPES
+def test_state_space_memory_with_shared_input_heads(dtype, h, g_, d, v):
+    """The matrix memory with per-token decay and input scale whose q and k heads are shared by groups of
+    heads, in portions through slots that change hands, against its restatement and the plain loop."""
+    g = torch.Generator().manual_seed(h * d + v)
+    state_ref = torch.randn(4, h, d * v, generator=g)
+    state_ref[[0, 2]] = 0
+    state = state_ref.clone().to(DEV)
+    pad = 3
+    for step, lens in enumerate(([21, 3], [1, 1], [2, 40], [1, 17])):
+        n = sum(lens)
+        wide = (0.6 * torch.randn(n, pad + 2 * g_ * d + h * v, generator=g)).to(dtype)
+        q, k, vv = wide[:, pad:pad + g_ * d], wide[:, pad + g_ * d:pad + 2 * g_ * d], wide[:, pad + 2 * g_ * d:]
+        cu, slots = _i32(np.concatenate([[0], np.cumsum(lens)])), _i32([2, 0])
+        a = torch.rand(n, h, generator=g) * 0.4 + 0.6
+        b = torch.rand(n, h, generator=g) + 0.1
+        want = torch.zeros(n, h * v)
+        R.matrix_recurrence(q, k, vv, h, d, v, state_ref, slots.cpu(), cu.cpu(), 2, want, act="silu", a=a, b=b,
+                            qk_heads=g_)
+        dw = wide.to(DEV)
+        got = torch.zeros(n, h * v, device=DEV)
+        _K().matrix_recurrence(dw[:, pad:pad + g_ * d], dw[:, pad + g_ * d:pad + 2 * g_ * d], dw[:, pad + 2 * g_ * d:],
+                               h, d, v, state, slots, cu, 2, got, act="silu", a=a.to(DEV), b=b.to(DEV), qk_heads=g_)
+        _close(got, want, torch.float32, f"step {step}")
+    _close(state, state_ref, torch.float32, "state")
+    assert torch.equal(state[[1, 3]].cpu(), state_ref[[1, 3]])
+
+
+@DTYPES
+def test_state_space_gates_and_gated_norm(dtype):
+    g = torch.Generator().manual_seed(4)
+    n, h = 19, 5
+    x = (2 * torch.randn(n, h + 6, generator=g)).to(dtype)
+    bias, alog = torch.randn(h, generator=g).to(dtype), (0.5 * torch.randn(h, generator=g)).to(dtype)
+    a, b = torch.zeros(n, h, device=DEV), torch.zeros(n, h, device=DEV)
+    _K().ssm_gates(x.to(DEV)[:, 3:3 + h], bias.to(DEV), alog.to(DEV), a, b)
+    dt = plain.softplus(x[:, 3:3 + h].double() + bias.double())
+    _close(b, dt, torch.float32, "step size")
+    _close(a, torch.exp(-torch.exp(alog.double()) * dt), torch.float32, "decay")
+    for c, hv, groups in ((18, 6, 3), (260, 65, 4), (70, 70, 1), (600, 100, 1), (3000, 250, 2)):
+        o = torch.randn(n, c, generator=g) * 2
+        xz = torch.randn(n, 2 * c + 4, generator=g).to(dtype)
+        w, skip = (1 + 0.3 * torch.randn(c, generator=g)).to(dtype), torch.randn(c // hv, generator=g).to(dtype)
+        want = torch.zeros(n, c, dtype=dtype)
+        R.gate_group_norm(o, groups, 1e-5, w, want, z=xz[:, c + 4:], skip=skip, x=xz[:, :c], x_act="silu", head_width=hv)
+        got = torch.zeros(n, c, dtype=dtype, device=DEV)
+        dxz = xz.to(DEV)
+        _K().gate_group_norm(o.to(DEV), groups, 1e-5, w.to(DEV), got, z=dxz[:, c + 4:], skip=skip.to(DEV), x=dxz[:, :c],
+                             x_act="silu", head_width=hv)
+        _close(got, want, dtype, f"width {c}")
+        y = (o.double() + skip.double().repeat_interleave(hv) * plain.silu(xz[:, :c].double())) * plain.silu(
+            xz[:, c + 4:].double())
+        y = plain.rms(y.view(n, groups, c // groups), 1e-5).reshape(n, c) * w.double()
+        _close(got, y, dtype, f"width {c} against the plain order: gate, then norm")
+
+
+@pytest.mark.parametrize("h,hk,d,v", [(4, 2, 8, 12), (3, 3, 33, 70), (1, 1, 8, 8), (6, 1, 4, 40), (2, 2, 64, 64),
+                                       (4, 2, 128, 128), (2, 1, 200, 24)])
+@DTYPES
+def test_delta_rule_memory_in_portions_through_slots_with_stale_contents(dtype, h, hk, d, v):
+    g = torch.Generator().manual_seed(h * d + v)
+    state_ref = torch.randn(4, h, d * v, generator=g)
+    state_ref[[0, 2]] = 0  # the two slots in use were zeroed when they were handed out
+    state = state_ref.clone().to(DEV)
+    gb, alog = torch.randn(h * d, generator=g).to(dtype), (0.5 * torch.randn(h, generator=g) - 1).to(dtype)
+    pad = 5
+    for step, lens in enumerate(([21, 3], [1, 1], [2, 40], [1, 70], [1, 1])):
+        n = sum(lens)
+        wide = (1.5 * torch.randn(n, pad + 2 * hk * d + h * v + h + 2, generator=g)).to(dtype)
+        at = [pad, pad + hk * d, pad + 2 * hk * d, pad + 2 * hk * d + h * v]
+        graw = torch.randn(n, h * d, generator=g)
+        cu, slots = _i32(np.concatenate([[0], np.cumsum(lens)])), _i32([2, 0])
+        want = torch.zeros(n, h * v)
+        R.delta_recurrence(wide[:, at[0]:at[1]], wide[:, at[1]:at[2]], wide[:, at[2]:at[3]], wide[:, at[3]:at[3] + h],
+                           graw, gb, alog, h, hk, d, v, state_ref, slots.cpu(), cu.cpu(), 2, want, q_scale=d ** -0.5)
+        dw = wide.to(DEV)
+        got = torch.zeros(n, h * v, device=DEV)
+        _K().delta_recurrence(dw[:, at[0]:at[1]], dw[:, at[1]:at[2]], dw[:, at[2]:at[3]], dw[:, at[3]:at[3] + h],
+                              graw.to(DEV), gb.to(DEV), alog.to(DEV), h, hk, d, v, state, slots, cu, 2, got,
+                              q_scale=d ** -0.5)
+        _close(got, want, torch.float32, f"step {step}", tol=1e-4)
+    _close(state, state_ref, torch.float32, "state", tol=1e-4)
+    assert torch.equal(state[[1, 3]].cpu(), state_ref[[1, 3]])  # slots of other requests are untouched
+
+
+def test_delta_rule_overwrites_what_a_key_held():
+    """With beta = 1, no decay and a unit key, writing v under k and reading with q = k returns v, whatever
+    the memory held under that key before; a key at a right angle is untouched."""
+    d, v = 16, 8
+    z = torch.zeros(3, 2 * d + v + 1)
+    big = 30.0  # silu(30) = 30; the unit norm takes the length away
+    z[:, 0] = big            # q = e0
+    z[0, d] = big            # k = e0, write v0
+    z[1, d + 1] = big        # k = e1, write v1
+    z[2, d] = big            # k = e0 again, write v2 over v0
+    vals = torch.tensor([[3.0] * v, [5.0] * v, [7.0] * v])
+    z[:, 2 * d:2 * d + v] = vals
+    z[:, -1] = 40.0  # beta = sigmoid(40) = 1
+    graw = torch.full((3, d), -60.0)  # softplus -> 0: no decay
+    state = torch.zeros(1, 1, d * v, device=DEV)
+    out = torch.zeros(3, v, device=DEV)
+    dz = z.to(DEV)
+    _K().delta_recurrence(dz[:, :d], dz[:, d:2 * d], dz[:, 2 * d:2 * d + v], dz[:, -1:], graw.to(DEV),
+                          torch.zeros(d, device=DEV), torch.zeros(1, device=DEV), 1, 1, d, v, state, _i32([0]),
+                          _i32([0, 3]), 1, out, q_scale=1.0)
+    silu = lambda t: t * torch.sigmoid(t)
+    assert torch.allclose(out[0].cpu(), silu(vals[0]), atol=1e-4)
+    assert torch.allclose(out[1].cpu(), silu(vals[0]), atol=1e-4)  # q = e0 still reads v0: k = e1 wrote elsewhere
+    assert torch.allclose(out[2].cpu(), silu(vals[2]), atol=1e-4)  # overwritten, not added
+
+
+@DTYPES
+@pytest.mark.parametrize("e,ident,top,ff,hid", [(5, 2, 2, 24, 48), (3, 0, 1, 16, 64), (9, 3, 4, 8, 40), (4, 1, 5, 40, 72),
+                                                 (40, 8, 6, 64, 128)])
+def test_ungated_experts_with_identity_experts_against_the_plain_router(dtype, e, ident, top, ff, hid):
+    from emberserve_b200.parts.base import StepContext
+    from emberserve_b200.parts.moe import RoutedMLP, RoutedMLPSpec
+
+    g = torch.Generator().manual_seed(e * top)
+    p = "m."
+    w = {p + "router": torch.randn(e + ident, hid, generator=g) * 0.3, p + "correction": 0.2 * torch.randn(e + ident, generator=g)}
+    for i in range(e):
+        w[f"{p}e{i}.up"] = torch.randn(ff, hid, generator=g) / math.sqrt(hid)
+        w[f"{p}e{i}.down"] = torch.randn(hid, ff, generator=g) / math.sqrt(ff)
+    w = {k: v.to(torch.bfloat16).float() for k, v in w.items()}
+    spec = RoutedMLPSpec(hidden=hid, intermediate=ff, num_experts=e, top_k=top, router_name=p + "router",
+                         expert_names=tuple((f"{p}e{i}.up", f"{p}e{i}.down") for i in range(e)), activation="gelu",
+                         identity_experts=ident, correction_name=p + "correction", route_scale=1.7)
+    part = RoutedMLP(spec, "ffn")
+    params = {}
+    for local, ps in part.param_specs().items():
+        t = torch.zeros(ps.shape)
+        for src in ps.sources:
+            (t if src.rows is None else t[src.rows[0]:src.rows[1]]).copy_(w[src.name])
+        params[local] = t.to(dtype).to(DEV)
+    part.bind(params)
+    bufs = {}
+
+    def scratch(name, shape, dt):
+        bufs[name] = torch.zeros(shape, dtype=dt, device=DEV)
+        return bufs[name]
+
+    for n in (1, 7, 130, 700):
+        x = torch.randn(n, hid, generator=g).to(dtype)
+        ctx = StepContext(num_tokens=n, num_rows=1, dtype=dtype, device=torch.device(DEV), tokens=None, positions=None,
+                          row_of_token=None, cu_q=None, starts=None, q_lens=[n], start_list=[0], scratch=scratch)
+        got = part.forward(x.to(DEV), ctx)
+        mlp = {"router": {"experts": e, "identity": ident, "top": top, "scale": 1.7}}
+        seen = []
+        want = plain.routed_ff(x.double(), {k: v.double() for k, v in w.items()}, p, mlp, seen)
+        choice, chosen = seen[0]
+        # rows whose choice is a near tie may choose otherwise in 32 bits: leave them out
+        kth = torch.topk(choice, min(top + 1, e + ident), dim=-1).values
+        clear = (kth[:, top - 1] - kth[:, top]) > (1e-4 if dtype == torch.float32 else 2e-2) if top < e + ident \
+            else torch.ones(n, dtype=torch.bool)
+        assert int(clear.sum()) >= n // 2
+        _close(got[clear.to(DEV)], want[clear], dtype, f"{n} tokens", tol=3e-5 if dtype == torch.float32 else 3e-2)
+        if ident:
+            assert bool((bufs["moe_ids"].view(n, top) >= e).any()), "no identity expert was ever chosen"
+
+
+# ---- one mechanism per model ------------------------------------------------------------------
+
+ONE_MIXER = {
+    "attention": tl._parallel(tl._left(6, 3, 8, 16, 3, 4, 30.0, 2.5, 0.9), tl._right(1, 4, 4, 1, 1, 1), None, 1.0, 0.01),
+    "attention_128": tl._parallel(tl._left(2, 1, 128, 128, 2, 64, 5000.0, 8.0), tl._right(1, 4, 4, 1, 1, 1), None, 1.0, 0.01),
+    "attention_wide_values": tl._parallel(tl._left(4, 2, 64, 128, 4, 32, 5000.0, 8.0), tl._right(1, 4, 4, 1, 1, 1), None, 1.0, 0.01),
+    "state_space": tl._parallel(tl._left(1, 1, 8, 8, 1, 0, 0.0, None), tl._right(6, 10, 12, 3, 2, 4), None, 0.01, 1.0),
+    "state_space_128": tl._parallel(tl._left(1, 1, 8, 8, 1, 0, 0.0, None), tl._right(4, 64, 128, 1, 1, 2), None, 0.01, 1.0),
+    "delta": tl._delta(4, 2, 12, 20, 3, (6, 5), None),
+    "delta_128": tl._delta(2, 2, 128, 128, 4, (16, 8), None),
+    "experts": tl._delta(1, 1, 4, 4, 1, (2, 2), tl._moe(24, 6, 2, 3, 2.0, 16)),
+    "dense": tl._delta(1, 1, 4, 4, 1, (2, 2), tl._dense(100)),
+}
+
+
+@DTYPES
+@pytest.mark.parametrize("which", sorted(ONE_MIXER))
+def test_one_layer_models_in_prompt_and_token_by_token(tmp_path, which, dtype):
+    cfg = {"architecture": "Lesosun", "vocab": 50, "width": 32, "norm": {"eps": 1e-5}, "max_positions": 256,
+           "residual_mult": 0.8, "layers": [ONE_MIXER[which]]}
+    model = tl.write_model(cfg, tmp_path / which, 31)
+    reqs = rc.make_requests(50, [45, 90], seed=1)
+    want = _oracle(model, reqs)
+    scale = max(float(np.abs(v).max()) for v in want.values())
+    for steps in (rc.whole(reqs), rc.bulk_then_tail(reqs, 90)):
+        got = _replay(model, None, dtype, steps, page_size=8)
+        _compare(got, want, reqs, scale, dtype, which)
+
+
+# ---- the engine -------------------------------------------------------------------------------
+
+def _oracle(model_dir, reqs):
+    cfg, w = plain.read_model_dir(model_dir)
+    return {rid: plain.forward(cfg, w, toks, torch.float64).numpy() for rid, toks in reqs}
+
+
+def _replay(model_dir, name, dtype, steps, slots=4, page_size=None):
+    from emberserve_b200.engine.replay import TraceReplayer
+    from emberserve_b200.engine.runner import ModelRunner
+
+    ps = page_size or tl.PAGE_SIZES[name]
+    pages = TraceReplayer.pages_for(rc.max_live_tokens(steps), ps)
+    runner = ModelRunner.from_dir(model_dir, dtype, page_size=ps, num_pages=pages, num_state_slots=slots)
+    rp = TraceReplayer(runner)
+    outs = {}
+    for s in steps:
+        o = rp.run_step(s)
+        if o is not None:
+            outs[s["step"]] = o
+        runner.cache.check()
+    st = runner.cache.stats()
+    assert st.num_sequences == 0 and st.num_free == st.num_pages and st.free_state_slots == st.num_state_slots
+    return rc.collect(steps, outs)
+
+
+def _compare(got, want, reqs, scale, dtype, what):
+    errs = np.array([float(np.abs(got[(rid, p)] - want[rid][p]).max()) for rid, toks in reqs
+                     for p in range(len(toks))]) / scale
+    if dtype == torch.float32:
+        assert errs.max() <= TOL32, f"{what}: max |dlogit| / scale {errs.max():.3e}"
+    else:
+        assert errs.max() <= TOL16 and np.median(errs) <= TOL16 / 4, (
+            f"{what}: max {errs.max():.3e}, median {np.median(errs):.3e}")
+
+
+@pytest.fixture(scope="module")
+def cases(les_dirs):
+    out = {}
+    for name in tl.ALL:
+        reqs = rc.make_requests(tl.ALL[name]["vocab"], LENGTHS[name], seed=7)
+        want = _oracle(les_dirs[name], reqs)
+        out[name] = (reqs, want, max(float(np.abs(v).max()) for v in want.values()))
+    return out
+
+
+@DTYPES
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("name", ["les_a", "les_b", "les_c"])
+def test_cut_equals_plain(les_dirs, cases, name, cut, dtype):
+    reqs, want, scale = cases[name]
+    steps = {"whole": rc.whole, "tail": lambda r: rc.bulk_then_tail(r, 40), "portions": rc.portions,
+             "mixed": lambda r: rc.mixed(r, seed=3)}[cut](reqs)
+    if cut == "mixed":
+        assert rc.max_live_tokens(steps) < sum(-(-len(t) // 64) * 64 for _, t in reqs)
+    got = _replay(les_dirs[name], name, dtype, steps)
+    assert len(got) == sum(len(t) for _, t in reqs)
+    _compare(got, want, reqs, scale, dtype, f"{name} {cut}")
+
+
+def test_batches_of_unequal_requests_equal_each_alone(les_dirs, cases):
+    """In 32 bits a request's logits in a mixed batch, through three state slots and a small pool
+    that seven requests share in turn, are those it has alone."""
+    name = "les_b"
+    reqs, want, scale = cases[name]
+    alone = _replay(les_dirs[name], name, torch.float32, rc.whole(reqs))
+    mixed = _replay(les_dirs[name], name, torch.float32, rc.mixed(reqs, max_live=3, seed=9), slots=3)
+    worst = max(float(np.abs(alone[k] - mixed[k]).max()) for k in alone)
+    assert worst <= TOL32 * scale
+
+
+@DTYPES
+def test_long_decoding_token_by_token(les_dirs, dtype):
+    """A whole request one token per step, from the first token on (zero states, empty convolutions, a
+    one-key softmax), across many pages."""
+    name = "les_a"
+    reqs = rc.make_requests(tl.ALL[name]["vocab"], [150], seed=21)
+    want = _oracle(les_dirs[name], reqs)
+    scale = float(np.abs(want["r0"]).max())
+    got = _replay(les_dirs[name], name, dtype, rc.bulk_then_tail(reqs, 150))
+    _compare(got, want, reqs, scale, dtype, "token by token")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(les_dirs, cases, tmp_path, dtype):
+    name = "les_c"
+    reqs, want, scale = cases[name]
+    steps = rc.mixed(reqs, seed=4)
+    out_dir = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(les_dirs[name]), "--dtype", dtype,
+         "--out", str(out_dir), "--max-tokens", str(rc.max_live_tokens(steps))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    vocab = tl.ALL[name]["vocab"]
+    outs = {s["step"]: np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab)
+            for s in steps if any(e["want"] for e in s["entries"])}
+    _compare(rc.collect(steps, outs), want, reqs, scale, torch.float32 if dtype == "float32" else torch.bfloat16,
+             "trace_run")
+
+
+def _plain_greedy(cfg, w, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(torch.argmax(plain.forward(cfg, w, toks, torch.float64)[-1])))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name", ["les_a", "les_b", "les_c"])
+def test_greedy_generation_through_the_entry_point(les_dirs, name):
+    from emberserve_b200 import LLM, SamplingParams
+
+    cfg, w = plain.read_model_dir(les_dirs[name])
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (1, 5, 11, 30)]
+    want = [_plain_greedy(cfg, w, p, 10) for p in prompts]
+    for how in (dict(), dict(max_num_batched_tokens=7), dict(enable_cuda_graphs=False, async_scheduling=False)):
+        llm = LLM(str(les_dirs[name]), dtype="float32", device=DEV, block_size=tl.PAGE_SIZES[name],
+                  num_gpu_blocks=256, max_model_len=128, max_num_seqs=3, **how)
+        got = [r.output_token_ids for r in llm.generate(prompts, SamplingParams.greedy(10, ignore_eos=True))]
+        assert got == want, how
+        st = llm.engine.runner.cache.stats()
+        assert st.num_free == st.num_pages and st.free_state_slots == st.num_state_slots
+
+
+def test_command_line_random_weights_then_generate(tmp_path):
+    """`random-weights` writes a Lesosun folder from its config.json; `generate` on it prints the
+    tokens that LLM.generate returns (sampled with a seed, bfloat16, decode steps from CUDA graphs)."""
+    from emberserve_b200 import LLM, SamplingParams
+
+    (tmp_path / "config.json").write_text(json.dumps(tl.LES_B))
+    model = tmp_path / "model"
+    proc = subprocess.run([sys.executable, "-m", "emberserve_b200", "random-weights", "--config",
+                           str(tmp_path / "config.json"), "--out", str(model), "--seed", "5", "--std", "0.3"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-1500:]
+    prompt = [7, 50, 33, 90, 9]
+    llm = LLM(str(model), dtype="bfloat16", device=DEV, block_size=16, num_gpu_blocks=64, max_model_len=200)
+    want = llm.generate([prompt], SamplingParams(max_tokens=6, temperature=0.7, top_k=20, seed=11))[0]
+    proc = subprocess.run(
+        [sys.executable, "-m", "emberserve_b200", "generate", "--model", str(model), "--dtype", "bfloat16",
+         "--block-size", "16", "--num-blocks", "64", "--max-model-len", "200", "--prompt-ids",
+         ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0.7", "--top-k", "20", "--seed", "11"],
+        capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-1500:]
+    assert [int(t) for t in proc.stdout.split()] == want.output_token_ids
