@@ -1032,6 +1032,65 @@ def run_vonulix(args) -> dict:
     return run_design_beside_qwen2(args, "vonulix", "Vonulix", args.vonulix_size, von, qwen, z, runs, others)
 
 
+# ---------------------------------------------------------------------------------------
+# --workload lesosun: the design with capped attention behind short convolutions beside a selective state
+# space, the channel-wise delta rule and ungated routed experts, beside Dedizen (its closest relative:
+# attention beside a matrix memory, recurrent layers) and the dense Qwen2 shape of equal width and layers.
+
+LESOSUN_SIZES = {
+    # width; attention heads / key heads / head size; state space heads x channels, state, groups; delta heads
+    # x dim x vdim and the inner sizes of its two-step projections; gated feed-forward; experts / identity /
+    # top / expert ff / shared ff
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ssm=(32, 64), state=128, groups=4, delta=(16, 128, 128),
+               ranks=(64, 64), ff=5504, experts=64, identity=4, top=6, expert_ff=1408, shared_ff=1408),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ssm=(64, 64), state=128, groups=8, delta=(32, 128, 128),
+               ranks=(128, 128), ff=10880, experts=32, identity=4, top=4, expert_ff=3072, shared_ff=3072),
+}
+
+
+def lesosun_config(size: str, vocab: int = 32000) -> dict:
+    """Six layers: parallel, delta, delta, parallel, delta, parallel; dense and routed feed-forwards in turn."""
+    z = LESOSUN_SIZES[size]
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.5}}
+    sh, sv = z["ssm"]
+    dh, dd, dv = z["delta"]
+
+    def parallel(mlp):
+        return {"type": "parallel", "mlp": mlp, "mixer": {
+            "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4,
+                     "scale": z["dim"] ** -0.5, "softcap": 30.0, "rot": {"base": 1000000.0, "dims": 64}},
+            "right": {"heads": sh, "vdim": sv, "state": z["state"], "groups": z["groups"], "norm_groups": 4, "conv": 4},
+            "left_scale": 0.7, "right_scale": 0.7}}
+
+    def delta(mlp):
+        return {"type": "channel_delta", "mlp": mlp, "mixer": {
+            "heads": dh, "kv_heads": dh, "dim": dd, "vdim": dv, "conv": 4, "decay_rank": z["ranks"][0],
+            "gate_rank": z["ranks"][1]}}
+
+    return {"architecture": "Lesosun", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5},
+            "residual_mult": 0.5, "logit_softcap": 30.0, "max_positions": 8192,
+            "layers": [parallel(dense), delta(moe), delta(dense), parallel(moe), delta(dense), parallel(dense)]}
+
+
+def run_lesosun(args) -> dict:
+    from emberserve_b200.config.dedizen import DedizenConfig
+    from emberserve_b200.config.lesosun import LesosunConfig
+    from emberserve_b200.config.model import Qwen2Config
+
+    z = LESOSUN_SIZES[args.lesosun_size]
+    les = LesosunConfig.from_dict(lesosun_config(args.lesosun_size))
+    runs = len(les.layers)
+    qwen = Qwen2Config.from_dict(dict(
+        SHAPE_7B, vocab_size=32000, hidden_size=z["width"], num_attention_heads=z["heads"],
+        num_key_value_heads=z["kv_heads"], head_dim=128, intermediate_size=z["ff"],
+        num_hidden_layers=runs, max_position_embeddings=8192, architectures=["Qwen2ForCausalLM"], model_type="qwen2"))
+    others = [("dedizen", "Dedizen", DedizenConfig.from_dict(dedizen_config(args.lesosun_size)))]
+    return run_design_beside_qwen2(args, "lesosun", "Lesosun", args.lesosun_size, les, qwen,
+                                   {k: (list(v) if isinstance(v, tuple) else v) for k, v in z.items()}, runs, others)
+
+
 def run_design_beside_qwen2(args, key: str, label: str, size: str, dam, qwen, z: dict, runs: int,
                             others: list | None = None) -> dict:
     """Prompt and decode steps of one design and of the dense Qwen2 shape beside it (and of `others`:
@@ -1159,7 +1218,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b", "damolorn", "dedizen", "vonulix"],
+    ap.add_argument("--workload", choices=["decode-7b", "serve-0.5b", "mixed-32b", "fp32-7b", "damolorn", "dedizen", "vonulix", "lesosun"],
                     default="decode-7b",
                     help="decode-7b: the headline line; serve-0.5b: continuous batching of --requests requests; "
                          "mixed-32b: chunked prefill of long prompts beside decode at the 32B shape; fp32-7b: "
@@ -1172,6 +1231,8 @@ def main() -> int:
     ap.add_argument("--damolorn-size", choices=sorted(DAMOLORN_SIZES), default="2k")
     ap.add_argument("--dedizen-size", choices=sorted(DEDIZEN_SIZES), default="2k")
     ap.add_argument("--vonulix-size", choices=sorted(VONULIX_SIZES), default="2k")
+    ap.add_argument("--lesosun-size", choices=sorted(LESOSUN_SIZES), default="2k",
+                    help="with --workload lesosun: layer sizes of the Lesosun design (beside Dedizen and Qwen2 at equal width)")
     ap.add_argument("--no-extras", action="store_true",
                     help="the headline line without the points that need other models or kernels alone")
     ap.add_argument("--requests", type=int, default=256)
@@ -1230,6 +1291,9 @@ def main() -> int:
         return 0
     if args.workload == "dedizen":
         print(json.dumps(run_dedizen(args)))
+        return 0
+    if args.workload == "lesosun":
+        print(json.dumps(run_lesosun(args)))
         return 0
     if args.workload == "vonulix":
         print(json.dumps(run_vonulix(args)))
