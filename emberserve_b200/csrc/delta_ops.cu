@@ -30,8 +30,7 @@ __device__ __forceinline__ float d_silu(float z) { return z / (1.f + expf(-z)); 
 
 // ---------------------------------------------------------------------------------------
 // residual += s0 d0 + s1 d1 + s2 d2;  r = rsqrt(mean(residual^2) + eps);  out1 = residual r g1;  out2 = residual r g2
-// (gains are read as stored plus `gain_offset`).  With `rows` only those rows are normed, compactly, after
-// the sum went into every row.
+// (gains are read as stored plus `gain_offset`); without outputs the sum alone.
 
 template <typename T>
 __global__ void add_scaled_norm2_kernel(const T* __restrict__ d0, const T* __restrict__ d1, const T* __restrict__ d2,
@@ -80,12 +79,16 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
 // ---------------------------------------------------------------------------------------
 // the delta-rule memory
 //
-// As in the matrix memory of recurrent.cu, a block of 16 warps owns a group of columns of one head's S
-// ([D, V]) for one request; a column is shared by SL lanes, lane s holding rows i * 4 SL + 4 s + e of
-// the column in registers.  Per tile of 32 tokens the block stages q, k (activation, unit norm, scale),
-// the decay of every key channel, v, beta and k.q in shared memory.  A column's update needs S^T k
-// before it can write, so that dot product closes with shuffles for every token; the read o = S^T q =
-// (g S)^T q + u (k.q) is linear in what a lane holds, so the lanes' shares are summed once per tile.
+// Two kernels.  ems::delta_prep_kernel computes, once per token, what the recurrence reads: q and k of
+// every q / k head (activation, unit norm, the query's scale), k . q, the decay of every head and key
+// channel, and beta; all 32-bit, in a work buffer [N, 2 HK D + H D + HK + H] (q | k | g | k.q | beta).
+// ems::delta_recurrence_kernel then walks the tokens: as in the matrix memory of recurrent.cu, a block of
+// 16 warps owns a group of columns of one head's S ([D, V]) for one request; a column is shared by SL
+// lanes, lane s holding rows i * 4 SL + 4 s + e of the column in registers.  Tiles of 32 tokens of q, k
+// and g are copied into shared memory with cp.async, the next tile while this one is computed.  A
+// column's update needs S^T k before it can write, so that dot product closes with shuffles for every
+// token; the read o = S^T q = (g S)^T q + u (k.q) is linear in what a lane holds, so the lanes' shares
+// are summed once per tile.
 
 constexpr int DR_WARPS = 16;
 constexpr int DR_TT = 32;
@@ -99,14 +102,66 @@ struct DeltaParams {
     const void* g_bias;        // [H * D]
     const void* a_log;         // [H]: g = exp(-exp(a_log[h]) * softplus(g_raw + g_bias))
     int p_dtype;               // element type of g_bias and a_log
+    float* work;               // [N, work_ld]: q [HK * D] | k [HK * D] | g [H * D] | k.q [HK] | beta [H]
+    int work_ld;
     float* state;              // [slots, H, D * V]
     const int* slots; const int* cu_q;
     float* out;                // [N, H * V] float
-    int H, HK, D, V, act, unit;
+    int H, HK, D, V, act, unit, vec_ok;
     float q_scale, unit_eps;
 };
 
 __device__ __forceinline__ float dr_in(float z, int act) { return act ? d_silu(z) : z; }
+
+// one block per token; a warp per head at a time
+template <typename T>
+__global__ void delta_prep_kernel(const DeltaParams p) {
+    const int tok = blockIdx.x, D = p.D;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    float* w = p.work + (size_t)tok * p.work_ld;
+    float* wq = w;
+    float* wk = wq + (size_t)p.HK * D;
+    float* wg = wk + (size_t)p.HK * D;
+    float* wkq = wg + (size_t)p.H * D;
+    float* wb = wkq + p.HK;
+    for (int j = warp; j < p.HK + p.H; j += nwarps) {
+        if (j < p.HK) {
+            const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)tok * p.ldq + (size_t)j * D;
+            const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)tok * p.ldk + (size_t)j * D;
+            float sq = 0.f, sk = 0.f, qk = 0.f;
+            for (int d = lane; d < D; d += 32) {
+                const float a = dr_in(to_f32<T>(qg[d]), p.act), b = dr_in(to_f32<T>(kg[d]), p.act);
+                sq = fmaf(a, a, sq);
+                sk = fmaf(b, b, sk);
+                qk = fmaf(a, b, qk);
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            qk = warp_sum(qk);
+            const float rq = (p.unit ? rsqrtf(sq + p.unit_eps) : 1.f) * p.q_scale;
+            const float rk = p.unit ? rsqrtf(sk + p.unit_eps) : 1.f;
+            for (int d = lane; d < D; d += 32) {
+                wq[(size_t)j * D + d] = dr_in(to_f32<T>(qg[d]), p.act) * rq;
+                wk[(size_t)j * D + d] = dr_in(to_f32<T>(kg[d]), p.act) * rk;
+            }
+            if (lane == 0) wkq[j] = qk * rq * rk;
+        } else {
+            const int h = j - p.HK;
+            const float neg_a = -expf(load_any(p.a_log, p.p_dtype, h));
+            for (int d = lane; d < D; d += 32) {
+                const size_t ch = (size_t)h * D + d;
+                wg[ch] = expf(neg_a * d_softplus(p.g_raw[(size_t)tok * ((size_t)p.H * D) + ch] + load_any(p.g_bias, p.p_dtype, ch)));
+            }
+            if (lane == 0) wb[h] = d_sigmoid(to_f32<T>(reinterpret_cast<const T*>(p.beta)[(size_t)tok * p.ldb + h]));
+        }
+    }
+}
+
+__device__ __forceinline__ void dr_cp16(float* dst, const float* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;   // (0: the 16 bytes are filled with zeros)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
 
 template <typename T, int DPT, int SL>
 __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const DeltaParams p) {
@@ -115,13 +170,8 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
     constexpr int DP = SL * DPT;
     constexpr int WCOLS = 32 / SL;
     constexpr int COLS = DR_WARPS * WCOLS;
+    constexpr int STAGE = 3 * TT * DP + TT * COLS + 2 * TT;   // floats of one stage
     extern __shared__ __align__(16) float smem[];
-    float* qs = smem;                 // [TT][DP]
-    float* ks = qs + TT * DP;         // [TT][DP]
-    float* gs = ks + TT * DP;         // [TT][DP]
-    float* vs = gs + TT * DP;         // [TT][COLS]
-    float* bs = vs + TT * COLS;       // [TT] beta
-    float* kqs = bs + TT;             // [TT] k . q
     const int D = p.D, V = p.V;
     const int row = blockIdx.z, head = blockIdx.y;
     const int kh = head / (p.H / p.HK);
@@ -139,58 +189,72 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
         const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
         S[i] = (live && d < D) ? st[(size_t)d * V + col] : 0.f;
     }
-    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)kh * D;
-    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)kh * D;
     const T* vg = reinterpret_cast<const T*>(p.v) + (size_t)head * V;
-    const float neg_a = -expf(load_any(p.a_log, p.p_dtype, head));
+    const size_t off_q = (size_t)kh * D, off_k = (size_t)p.HK * D + (size_t)kh * D;
+    const size_t off_g = 2 * (size_t)p.HK * D + (size_t)head * D;
+    const size_t off_kq = 2 * (size_t)p.HK * D + (size_t)p.H * D + kh, off_b = 2 * (size_t)p.HK * D + (size_t)p.H * D + p.HK + head;
 
-    for (int t0 = 0; t0 < qlen; t0 += TT) {
+    // Stage the tile that begins at token t0: q, k, g rows (zeros past D; tokens past the end hold q = k = 0,
+    // g = 1, beta = 0: nothing changes), v of this block's columns, k.q and beta.
+    auto stage = [&](int t0, float* buf) {
         const int cnt = min(TT, qlen - t0);
-        __syncthreads();  // the tile before is consumed
-        for (int idx = threadIdx.x; idx < TT * DP; idx += THREADS) {
-            const int t = idx / DP, d = idx % DP;
-            float qv = 0.f, kv = 0.f, gv = 1.f;
-            if (t < cnt && d < D) {
-                const size_t tok = (size_t)(q0 + t0 + t);
-                qv = dr_in(to_f32<T>(qg[tok * p.ldq + d]), p.act);
-                kv = dr_in(to_f32<T>(kg[tok * p.ldk + d]), p.act);
-                const size_t ch = (size_t)head * D + d;
-                gv = expf(neg_a * d_softplus(p.g_raw[tok * ((size_t)p.H * D) + ch] + load_any(p.g_bias, p.p_dtype, ch)));
+        float* qs = buf;
+        float* ks = qs + TT * DP;
+        float* gs = ks + TT * DP;
+        float* vs = gs + TT * DP;
+        float* bs = vs + TT * COLS;
+        float* kqs = bs + TT;
+        if (p.vec_ok) {
+            for (int idx = threadIdx.x; idx < TT * (DP / 4); idx += THREADS) {
+                const int t = idx / (DP / 4), d = (idx % (DP / 4)) * 4;
+                const bool ok = t < cnt && d < D;
+                const float* w = p.work + (size_t)(q0 + t0 + (ok ? t : 0)) * p.work_ld + (ok ? d : 0);
+                dr_cp16(qs + t * DP + d, w + off_q, ok);
+                dr_cp16(ks + t * DP + d, w + off_k, ok);
+                if (t < cnt && d >= D) *reinterpret_cast<float4*>(gs + t * DP + d) = make_float4(1.f, 1.f, 1.f, 1.f);
+                else if (t >= cnt) *reinterpret_cast<float4*>(gs + t * DP + d) = make_float4(1.f, 1.f, 1.f, 1.f);
+                else dr_cp16(gs + t * DP + d, w + off_g, true);
             }
-            qs[idx] = qv;
-            ks[idx] = kv;
-            gs[idx] = gv;
+        } else {
+            for (int idx = threadIdx.x; idx < TT * DP; idx += THREADS) {
+                const int t = idx / DP, d = idx % DP;
+                const bool ok = t < cnt && d < D;
+                const float* w = p.work + (size_t)(q0 + t0 + (ok ? t : 0)) * p.work_ld + (ok ? d : 0);
+                qs[idx] = ok ? w[off_q] : 0.f;
+                ks[idx] = ok ? w[off_k] : 0.f;
+                gs[idx] = ok ? w[off_g] : 1.f;
+            }
         }
+        asm volatile("cp.async.commit_group;\n" ::);
         for (int idx = threadIdx.x; idx < TT * COLS; idx += THREADS) {
             const int t = idx / COLS, gc = blockIdx.x * COLS + idx % COLS;
             vs[idx] = (t < cnt && gc < V) ? dr_in(to_f32<T>(vg[(size_t)(q0 + t0 + t) * p.ldv + gc]), p.act) : 0.f;
         }
-        __syncthreads();
-        // unit vectors, the query's scale, k . q and beta: a warp per token
-        for (int t = warp; t < TT; t += DR_WARPS) {
-            float sq = 0.f, sk = 0.f;
-            for (int d = lane; d < DP; d += 32) {
-                sq = fmaf(qs[t * DP + d], qs[t * DP + d], sq);
-                sk = fmaf(ks[t * DP + d], ks[t * DP + d], sk);
-            }
-            sq = warp_sum(sq);
-            sk = warp_sum(sk);
-            const float rq = (p.unit ? rsqrtf(sq + p.unit_eps) : 1.f) * p.q_scale;
-            const float rk = p.unit ? rsqrtf(sk + p.unit_eps) : 1.f;
-            float kq = 0.f;
-            for (int d = lane; d < DP; d += 32) {
-                const float a = qs[t * DP + d] * rq, b = ks[t * DP + d] * rk;
-                qs[t * DP + d] = a;
-                ks[t * DP + d] = b;
-                kq = fmaf(a, b, kq);
-            }
-            kq = warp_sum(kq);
-            if (lane == 0) {
-                kqs[t] = kq;
-                bs[t] = t < cnt ? d_sigmoid(to_f32<T>(reinterpret_cast<const T*>(p.beta)[(size_t)(q0 + t0 + t) * p.ldb + head])) : 0.f;
-            }
+        if ((int)threadIdx.x < TT) {
+            const int t = threadIdx.x;
+            const float* w = p.work + (size_t)(q0 + t0 + (t < cnt ? t : 0)) * p.work_ld;
+            bs[t] = t < cnt ? w[off_b] : 0.f;
+            kqs[t] = t < cnt ? w[off_kq] : 0.f;
+        }
+    };
+
+    stage(0, smem);
+    int cur = 0;
+    for (int t0 = 0; t0 < qlen; t0 += TT, cur ^= 1) {
+        const int cnt = min(TT, qlen - t0);
+        if (t0 + TT < qlen) {
+            stage(t0 + TT, smem + (cur ^ 1) * STAGE);   // in flight while this tile is computed
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
+        const float* qs = smem + cur * STAGE;
+        const float* ks = qs + TT * DP;
+        const float* gs = ks + TT * DP;
+        const float* vs = gs + TT * DP;
+        const float* bs = vs + TT * COLS;
+        const float* kqs = bs + TT;
         float acc[TT];
 #pragma unroll
         for (int t = 0; t < TT; ++t) {
@@ -247,6 +311,7 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
                 if (t < cnt) p.out[(size_t)(q0 + t0 + t) * ((size_t)p.H * V) + (size_t)head * V + col] = acc[j];
             }
         }
+        __syncthreads();  // this tile is consumed before the stage after next overwrites it
     }
     if (live) {
 #pragma unroll
@@ -262,53 +327,46 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
 // consecutive floats of every row.
 template <typename T>
 __global__ void __launch_bounds__(128) delta_step_kernel(const DeltaParams p) {
-    __shared__ float qs[256], ks[256], gs[256], red[33];
+    __shared__ float qs[256], ks[256], gs[256];
     const int D = p.D, V = p.V;
     const int tok = blockIdx.z, head = blockIdx.y;   // (row r brings token r)
     const int kh = head / (p.H / p.HK);
-    const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)tok * p.ldq + (size_t)kh * D;
-    const T* kg = reinterpret_cast<const T*>(p.k) + (size_t)tok * p.ldk + (size_t)kh * D;
-    const float neg_a = -expf(load_any(p.a_log, p.p_dtype, head));
-    float sq = 0.f, sk = 0.f;
+    const float* w = p.work + (size_t)tok * p.work_ld;
+    const float* wq = w + (size_t)kh * D;
+    const float* wk = w + (size_t)p.HK * D + (size_t)kh * D;
+    const float* wg = w + 2 * (size_t)p.HK * D + (size_t)head * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float a = dr_in(to_f32<T>(qg[d]), p.act), b = dr_in(to_f32<T>(kg[d]), p.act);
-        qs[d] = a;
-        ks[d] = b;
-        sq = fmaf(a, a, sq);
-        sk = fmaf(b, b, sk);
-        const size_t ch = (size_t)head * D + d;
-        gs[d] = expf(neg_a * d_softplus(p.g_raw[(size_t)tok * ((size_t)p.H * D) + ch] + load_any(p.g_bias, p.p_dtype, ch)));
+        qs[d] = wq[d];
+        ks[d] = wk[d];
+        gs[d] = wg[d];
     }
-    sq = block_sum(sq, red);
-    sk = block_sum(sk, red);
-    const float rq = (p.unit ? rsqrtf(sq + p.unit_eps) : 1.f) * p.q_scale;
-    const float rk = p.unit ? rsqrtf(sk + p.unit_eps) : 1.f;
+    __syncthreads();
     const int col = blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= V) return;
-    const float beta = d_sigmoid(to_f32<T>(reinterpret_cast<const T*>(p.beta)[(size_t)tok * p.ldb + head]));
+    const float beta = w[2 * (size_t)p.HK * D + (size_t)p.H * D + p.HK + head];
     const float vj = dr_in(to_f32<T>(reinterpret_cast<const T*>(p.v)[(size_t)tok * p.ldv + (size_t)head * V + col]), p.act);
     float* sp = p.state + ((size_t)p.slots[tok] * p.H + head) * ((size_t)D * V) + col;
     float dk0 = 0.f, dk1 = 0.f;
     int d = 0;
     for (; d + 1 < D; d += 2) {
-        dk0 = fmaf(gs[d] * sp[(size_t)d * V], ks[d] * rk, dk0);
-        dk1 = fmaf(gs[d + 1] * sp[(size_t)(d + 1) * V], ks[d + 1] * rk, dk1);
+        dk0 = fmaf(gs[d] * sp[(size_t)d * V], ks[d], dk0);
+        dk1 = fmaf(gs[d + 1] * sp[(size_t)(d + 1) * V], ks[d + 1], dk1);
     }
-    if (d < D) dk0 = fmaf(gs[d] * sp[(size_t)d * V], ks[d] * rk, dk0);
+    if (d < D) dk0 = fmaf(gs[d] * sp[(size_t)d * V], ks[d], dk0);
     const float u = beta * (vj - (dk0 + dk1));
     float o0 = 0.f, o1 = 0.f;
     for (d = 0; d + 1 < D; d += 2) {
-        const float s0 = fmaf(ks[d] * rk, u, gs[d] * sp[(size_t)d * V]);
-        const float s1 = fmaf(ks[d + 1] * rk, u, gs[d + 1] * sp[(size_t)(d + 1) * V]);
+        const float s0 = fmaf(ks[d], u, gs[d] * sp[(size_t)d * V]);
+        const float s1 = fmaf(ks[d + 1], u, gs[d + 1] * sp[(size_t)(d + 1) * V]);
         sp[(size_t)d * V] = s0;
         sp[(size_t)(d + 1) * V] = s1;
-        o0 = fmaf(s0, qs[d] * rq, o0);
-        o1 = fmaf(s1, qs[d + 1] * rq, o1);
+        o0 = fmaf(s0, qs[d], o0);
+        o1 = fmaf(s1, qs[d + 1], o1);
     }
     if (d < D) {
-        const float s0 = fmaf(ks[d] * rk, u, gs[d] * sp[(size_t)d * V]);
+        const float s0 = fmaf(ks[d], u, gs[d] * sp[(size_t)d * V]);
         sp[(size_t)d * V] = s0;
-        o0 = fmaf(s0, qs[d] * rq, o0);
+        o0 = fmaf(s0, qs[d], o0);
     }
     p.out[(size_t)tok * ((size_t)p.H * V) + (size_t)head * V + col] = o0 + o1;
 }
@@ -317,7 +375,7 @@ template <typename T, int DPT, int SL>
 static int launch_delta_as(const DeltaParams& p, int rows, cudaStream_t stream) {
     constexpr int COLS = DR_WARPS * (32 / SL);
     const dim3 grid((p.V + COLS - 1) / COLS, p.H, rows);
-    const size_t smem = sizeof(float) * ((size_t)DR_TT * (3 * SL * DPT + COLS) + 2 * DR_TT);
+    const size_t smem = sizeof(float) * 2 * ((size_t)DR_TT * (3 * SL * DPT + COLS) + 2 * DR_TT);
     auto kernel = delta_recurrence_kernel<T, DPT, SL>;
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -327,11 +385,16 @@ static int launch_delta_as(const DeltaParams& p, int rows, cudaStream_t stream) 
 }
 
 template <typename T>
-static int launch_delta(const DeltaParams& p, int rows, int N, cudaStream_t stream) {
+static int launch_delta(DeltaParams& p, int rows, int N, cudaStream_t stream) {
+    const int units = p.HK + p.H;
+    delta_prep_kernel<T><<<N, 32 * (units < 8 ? units : 8), 0, stream>>>(p);
+    if (launch_status() != EMS_OK) return EMS_ERR_LAUNCH;
     if (N == rows) {
         delta_step_kernel<T><<<dim3((p.V + 127) / 128, p.H, rows), 128, 0, stream>>>(p);
         return launch_status();
     }
+    // 16-byte copies of four floats where every row of the work buffer begins aligned
+    p.vec_ok = p.D % 4 == 0 && p.work_ld % 4 == 0 && ((uintptr_t)p.work % 16) == 0;
     if (p.D <= 32) return launch_delta_as<T, 4, 8>(p, rows, stream);
     if (p.D <= 64) return launch_delta_as<T, 4, 16>(p, rows, stream);
     if (p.D <= 128) return launch_delta_as<T, 4, 32>(p, rows, stream);
@@ -436,17 +499,26 @@ EMS_EXPORT int ems_delta_recurrence(const void* q, long long ldq, const void* k,
                                     long long ldv, const void* beta, long long ldb, int dtype, int act, int unit,
                                     float unit_eps, float q_scale, const float* g_raw, const void* g_bias,
                                     const void* a_log, int p_dtype, float* state, const int* slots, const int* cu_q,
-                                    int rows, int N, int H, int HK, int D, int V, float* out, cudaStream_t stream) {
+                                    int rows, int N, int H, int HK, int D, int V, float* out, float* work,
+                                    long long work_floats, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return EMS_OK;
     if (H <= 0 || HK <= 0 || H % HK || D <= 0 || D > 256 || V <= 0 || H > 65535 || rows > 65535) return EMS_ERR_SHAPE;
+    // a row of the work buffer: q | k | g | k.q | beta, rounded up to a multiple of four floats
+    const int work_ld = (2 * HK * D + H * D + HK + H + 3) / 4 * 4;
+    if (!work || work_floats < (long long)N * work_ld) return EMS_ERR_SCRATCH;
     DeltaParams p;
     p.q = q; p.k = k; p.v = v; p.ldq = ldq; p.ldk = ldk; p.ldv = ldv; p.beta = beta; p.ldb = ldb; p.g_raw = g_raw;
     p.g_bias = g_bias; p.a_log = a_log; p.p_dtype = p_dtype; p.state = state; p.slots = slots; p.cu_q = cu_q;
     p.out = out; p.H = H; p.HK = HK; p.D = D; p.V = V; p.act = act; p.unit = unit; p.q_scale = q_scale;
-    p.unit_eps = unit_eps;
+    p.unit_eps = unit_eps; p.work = work; p.work_ld = work_ld; p.vec_ok = 0;
     if (dtype == EMS_F32) return launch_delta<float>(p, rows, N, stream);
     if (dtype == EMS_BF16) return launch_delta<bf16>(p, rows, N, stream);
     return EMS_ERR_DTYPE;
+}
+
+// floats of the work buffer that ems_delta_recurrence needs for N tokens
+EMS_EXPORT long long ems_delta_work_floats(int N, int H, int HK, int D) {
+    return (long long)N * ((2 * HK * D + H * D + HK + H + 3) / 4 * 4);
 }
 
 EMS_EXPORT int ems_ssm_gates(const void* x, long long ldx, int dtype, const void* bias, const void* a_log, int p_dtype,

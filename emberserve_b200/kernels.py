@@ -103,7 +103,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_add_scaled_norm2": [P, P, P, F, F, F, P, P, P, I, F, F, P, P, I, I, I, P],
         "ems_stream_norm": [P, P, I, F, F, I, I, P],
         "ems_softcap": [P, L, F, P],
-        "ems_delta_recurrence": [P, L, P, L, P, L, P, L, I, I, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P, P],
+        "ems_delta_recurrence": [P, L, P, L, P, L, P, L, I, I, I, F, F, P, P, P, I, P, P, P, I, I, I, I, I, I, P, P, L, P],
         "ems_ssm_gates": [P, L, I, P, P, I, P, P, I, I, P],
         "ems_gate_group_norm": [P, P, L, I, P, P, L, P, I, P, I, I, I, I, I, F, P],
     }
@@ -125,6 +125,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ems_latent_attention_scratch_bytes.restype = c_longlong
     lib.ems_moe_tile_rows.argtypes = []
     lib.ems_moe_tile_rows.restype = c_int
+    lib.ems_delta_work_floats.argtypes = [I, I, I, I]
+    lib.ems_delta_work_floats.restype = c_longlong
 
 
 _sm_counts: dict[int, int] = {}
@@ -951,7 +953,8 @@ def softcap(x: torch.Tensor, cap: float) -> None:
 def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, g_raw: torch.Tensor,
                      g_bias: torch.Tensor, a_log: torch.Tensor, num_heads: int, qk_heads: int, dim: int, vdim: int,
                      state: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, num_rows: int, out: torch.Tensor,
-                     act: str = "silu", unit_eps: float | None = 1e-6, q_scale: float = 1.0) -> None:
+                     act: str = "silu", unit_eps: float | None = 1e-6, q_scale: float = 1.0,
+                     work: torch.Tensor | None = None) -> None:
     """A matrix memory per head written by the delta rule with a decay per key channel, run over every
     request's tokens in order:
 
@@ -961,7 +964,9 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
     fine), each of q, k, v passed through `act`; with `unit_eps` q and k become x / sqrt(sum(x^2) + unit_eps)
     per head; q is multiplied by `q_scale`; beta_t = sigmoid(beta[t, h]); g_t = exp(-exp(a_log[h]) *
     softplus(g_raw[t, h * dim + d] + g_bias[h * dim + d])) with g_raw float32 [N, H * dim].  Head h reads
-    q / k head h // (H / qk_heads).  state: float32 [slots, H, dim * vdim]; out: float32 [N, H * vdim]."""
+    q / k head h // (H / qk_heads).  state: float32 [slots, H, dim * vdim]; out: float32 [N, H * vdim].
+    `work`: float32, at least `delta_work_floats(N, H, qk_heads, dim)` elements, where a first kernel leaves
+    the prepared q, k, decays, k . q and beta of every token (allocated here when None)."""
     n = q.shape[0]
     assert q.stride(1) == k.stride(1) == v.stride(1) == beta.stride(1) == 1 and q.dtype == k.dtype == v.dtype == beta.dtype
     assert out.dtype == torch.float32 and out.shape == (n, num_heads * vdim) and out.is_contiguous()
@@ -970,12 +975,19 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
     assert g_bias.numel() == num_heads * dim and a_log.numel() == num_heads and g_bias.dtype == a_log.dtype
     if not q.is_cuda:
         raise KernelError("q must be a CUDA tensor (emberserve_b200 has no CPU path)")
+    if work is None:
+        work = torch.empty(delta_work_floats(n, num_heads, qk_heads, dim), dtype=torch.float32, device=q.device)
     _check(library().ems_delta_recurrence(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), beta.data_ptr(),
         beta.stride(0), _dt(q), MEMORY_INPUT_ACTIVATIONS[act], 0 if unit_eps is None else 1, float(unit_eps or 0.0),
         float(q_scale), _f32(g_raw, "g_raw"), _ptr(g_bias, "g_bias"), _ptr(a_log, "a_log"), _dt(a_log),
         _ptr(state, "state"), _i32(slots, "slots"), _i32(cu_q, "cu_q"), num_rows, n, num_heads, qk_heads, dim, vdim,
-        _ptr(out, "out"), _stream()), "delta_recurrence")
+        _ptr(out, "out"), _f32(work, "work"), work.numel(), _stream()), "delta_recurrence", 2)
+
+
+def delta_work_floats(num_tokens: int, num_heads: int, qk_heads: int, dim: int) -> int:
+    """Elements of the float32 work buffer that `delta_recurrence` needs for `num_tokens` tokens."""
+    return int(library().ems_delta_work_floats(num_tokens, num_heads, qk_heads, dim))
 
 
 def ssm_gates(x: torch.Tensor, bias: torch.Tensor, a_log: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> None:

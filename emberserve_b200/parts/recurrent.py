@@ -465,6 +465,8 @@ class ChannelDelta(Mixer):
             prefix + ".conv", self.shared)
         self._conv_state = self.conv.cache_need()
         self._norm_rows: torch.Tensor | None = None
+        # 32-bit numbers per token that the memory kernel prepares: q | k | decays | k.q | beta, in fours
+        self._work_per_token = -(-(2 * self.qk + spec.num_heads * spec.dim + spec.qk_heads + spec.num_heads) // 4) * 4
 
     def children(self) -> dict[str, Part]:
         return {"conv": self.conv}
@@ -500,7 +502,7 @@ class ChannelDelta(Mixer):
 
     def scratch_elements_per_token(self) -> int:
         s: ChannelDeltaSpec = self.spec
-        return self.cols + 2 * s.num_heads * s.dim + 5 * self.vv + s.hidden
+        return self.cols + 2 * s.num_heads * s.dim + 5 * self.vv + s.hidden + 2 * self._work_per_token
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         s: ChannelDeltaSpec = self.spec
@@ -514,9 +516,11 @@ class ChannelDelta(Mixer):
         gate = ctx.scratch("delta_gate", (n, vv), ctx.dtype)
         linear(proj[:, self.g_at:self.g_at + s.gate_rank], self.wg2, None, gate, ctx.scratch)
         read = ctx.scratch("memory_read", (n, vv), torch.float32)
+        work = ctx.scratch("delta_work", (n * self._work_per_token,), torch.float32)
         K.delta_recurrence(qkv[:, :qk], qkv[:, qk:2 * qk], qkv[:, 2 * qk:], proj[:, self.b_at:self.b_at + h], g_raw,
                            self.dt_bias, self.a_log, h, s.qk_heads, s.dim, s.vdim, state.state, state.slots,
-                           ctx.cu_q, ctx.num_rows, read, act="silu", unit_eps=s.unit_eps, q_scale=s.dim ** -0.5)
+                           ctx.cu_q, ctx.num_rows, read, act="silu", unit_eps=s.unit_eps, q_scale=s.dim ** -0.5,
+                           work=work)
         gated = ctx.scratch("memory_gated", (n, vv), ctx.dtype)
         K.group_norm_gate(read, h, s.eps, self._norm_rows, gate, gated)
         y = ctx.scratch("memory_out", (n, s.hidden), ctx.dtype)

@@ -696,7 +696,7 @@ def softcap(x, cap):
 
 
 def delta_recurrence(q, k, v, beta, g_raw, g_bias, a_log, num_heads, qk_heads, dim, vdim, state, slots, cu_q,
-                     num_rows, out, act="silu", unit_eps=1e-6, q_scale=1.0):
+                     num_rows, out, act="silu", unit_eps=1e-6, q_scale=1.0, work=None):
     n, H, G, D, V = q.shape[0], num_heads, qk_heads, dim, vdim
     qq = _memory_act(q[:, :G * D].float(), act).view(n, G, D)
     kk = _memory_act(k[:, :G * D].float(), act).view(n, G, D)
