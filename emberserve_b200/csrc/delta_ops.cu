@@ -440,14 +440,31 @@ __global__ void gate_group_norm_kernel(const float* __restrict__ o, const T* __r
         if (z) y *= d_silu(to_f32<T>(z[(size_t)tok * ldz + ch]));
         return y;
     };
+    // (a thread's first eight values stay in registers between the two passes)
+    constexpr int KEEP = 8;
+    float kept[KEEP];
     float ss = 0.f;
-    for (int c = lane; c < gs; c += width) {
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const int c = lane + i * width;
+        kept[i] = c < gs ? value(g * gs + c) : 0.f;
+        ss = fmaf(kept[i], kept[i], ss);
+    }
+    for (int c = lane + KEEP * width; c < gs; c += width) {
         const float y = value(g * gs + c);
         ss = fmaf(y, y, ss);
     }
     ss = BLOCK ? block_sum(ss, red) : warp_sum(ss);
     const float r = rsqrtf(ss / gs + eps);
-    for (int c = lane; c < gs; c += width) {
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+        const int c = lane + i * width;
+        if (c < gs) {
+            const int ch = g * gs + c;
+            out[(size_t)tok * C + ch] = from_f32<T>(kept[i] * r * load_any(w, w_dtype, ch));
+        }
+    }
+    for (int c = lane + KEEP * width; c < gs; c += width) {
         const int ch = g * gs + c;
         out[(size_t)tok * C + ch] = from_f32<T>(value(ch) * r * load_any(w, w_dtype, ch));
     }

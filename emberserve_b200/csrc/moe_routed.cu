@@ -527,12 +527,16 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
 // null: every weight 1), plus extra[t, :] (optional)
 __global__ void moe_combine_rows_kernel(const bf16* __restrict__ y, const int* __restrict__ inv,
                                         const float* __restrict__ wts, bf16* __restrict__ out, int top, int H,
-                                        const bf16* __restrict__ extra) {
+                                        const bf16* __restrict__ extra, const int* __restrict__ ids,
+                                        const bf16* __restrict__ x, int num_real) {
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k)
-            s = fmaf(wts ? wts[t * top + k] : 1.f, __bfloat162float(y[(size_t)inv[t * top + k] * H + c]), s);
+        for (int k = 0; k < top; ++k) {
+            const bool same = ids && ids[t * top + k] >= num_real;   // an expert that returns its input
+            s = fmaf(wts ? wts[t * top + k] : 1.f,
+                     __bfloat162float(same ? x[t * H + c] : y[(size_t)inv[t * top + k] * H + c]), s);
+        }
         if (extra) s += __bfloat162float(extra[t * H + c]);
         out[t * H + c] = __float2bfloat16_rn(s);
     }
@@ -543,11 +547,13 @@ __global__ void moe_combine_rows_kernel(const bf16* __restrict__ y, const int* _
 using namespace ems;
 
 EMS_EXPORT int ems_moe_combine_rows(const void* y, const int* inv, const float* wts, void* out, int n, int top, int H,
-                                    const void* extra, cudaStream_t stream) {
+                                    const void* extra, const int* ids, const void* x, int num_real,
+                                    cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     int th = 32;
     while (th < H && th < 256) th <<= 1;
-    moe_combine_rows_kernel<<<n, th, 0, stream>>>((const bf16*)y, inv, wts, (bf16*)out, top, H, (const bf16*)extra);
+    moe_combine_rows_kernel<<<n, th, 0, stream>>>((const bf16*)y, inv, wts, (bf16*)out, top, H, (const bf16*)extra,
+                                                  x ? ids : nullptr, (const bf16*)x, num_real);
     return launch_status();
 }
 

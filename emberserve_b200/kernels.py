@@ -91,7 +91,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "ems_heads_gate": [P, P, I, P, I, I, I, I, P],
         "ems_moe_route": [P, I, I, I, I, P, P, P, P, P, I, I, P, I, P, I, P, F, F, I, P],
         "ems_moe_down_grouped_tc05": [P, P, P, I, I, I, I, P, P],
-        "ems_moe_combine_rows": [P, P, P, P, I, I, I, P, P],
+        "ems_moe_combine_rows": [P, P, P, P, I, I, I, P, P, P, I, P],
         "ems_moe_gather": [P, P, I, I, I, P, P],
         "ems_moe_up_grouped_tc05": [P, P, P, I, I, I, I, P, P, P, I, F, F, P],
         "ems_moe_up": [P, P, I, P, P, I, I, I, I, I, P, I, P, F, F, I, P],
@@ -613,15 +613,19 @@ def moe_down_grouped_tc05(act: torch.Tensor, wdown: torch.Tensor, big: torch.Ten
 
 
 def moe_combine_rows(y: torch.Tensor, inv: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor, top: int,
-                     extra: torch.Tensor | None = None) -> None:
+                     extra: torch.Tensor | None = None, ids: torch.Tensor | None = None, x: torch.Tensor | None = None,
+                     num_real: int = 0) -> None:
     """out[t, :] = sum_k weights[t, k] * y[inv[t * top + k], :] (k ascending; every weight 1 when `weights` is
-    None) + extra[t, :] (optional) for bfloat16 rows `y` in the sorted layout."""
+    None) + extra[t, :] (optional) for bfloat16 rows `y` in the sorted layout.  With `ids`, `x` and `num_real`
+    a choice whose expert id is at or past `num_real` contributes x[t] instead (as in `moe_combine`)."""
     n, h = out.shape
     assert y.dtype == out.dtype == torch.bfloat16 and y.shape[1] == h
     assert weights is None or weights.dtype == torch.float32
     assert extra is None or (extra.dtype == out.dtype and extra.shape == out.shape)
+    assert x is None or (ids is not None and x.dtype == out.dtype and x.shape == out.shape and x.is_contiguous())
     _check(library().ems_moe_combine_rows(_ptr(y, "y"), _i32(inv, "inv"), _ptr(weights, "weights"), _ptr(out, "out"),
-                                          n, top, h, _ptr(extra, "extra"), _stream()), "moe_combine_rows")
+                                          n, top, h, _ptr(extra, "extra"), None if x is None else _i32(ids, "ids"),
+                                          _ptr(x, "x"), int(num_real), _stream()), "moe_combine_rows")
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor, top: int,

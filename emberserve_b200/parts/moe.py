@@ -234,7 +234,9 @@ class RoutedMLP(FeedForward):
 
     def scratch_elements_per_token(self) -> int:
         s: RoutedMLPSpec = self.spec
-        return s.top_k * (s.intermediate + 2 * s.hidden) + 4 * s.hidden + 2 * self.total
+        # activations of the chosen experts, their 32-bit outputs (two elements each), the result; in prompt
+        # steps the gathered rows as well, and the padding of both to tiles of 256 rows
+        return 2 * s.top_k * (s.intermediate + 2 * s.hidden) + 4 * s.hidden + 2 * self.total
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s: RoutedMLPSpec = self.spec
@@ -258,17 +260,37 @@ class RoutedMLP(FeedForward):
             # (its result stays in a buffer of its own until the routed experts' sum takes it in)
             extra = ctx.scratch("ffn_shared", (n, s.hidden), ctx.dtype)
             extra.copy_(self.shared_ffn.forward(x, ctx))
-        K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles,
-                    correction=self._correction32, renorm_eps=s.renorm_eps, scale=s.route_scale,
-                    plan_experts=s.num_experts)
+        routing = dict(correction=self._correction32, renorm_eps=s.renorm_eps, scale=s.route_scale,
+                       plan_experts=s.num_experts)
+        same = dict(ids=ids, x=x, num_real=s.num_experts) if s.identity_experts else {}
+        if (x.is_cuda and ctx.dtype == torch.bfloat16 and n > _GROUPED_TC05_TOKENS and s.intermediate % 8 == 0
+                and s.hidden % 8 == 0):
+            # Prompt steps in bfloat16: every expert's sorted rows start at a multiple of 256, the rows are
+            # gathered into that layout and both products run on the grouped tcgen05 kernel (groups of
+            # identity experts belong to nobody and are skipped); the activation is a pass of its own.
+            big_rows = K.MOE_BIG_TILE_ROWS
+            big = ctx.scratch("moe_big", (K.moe_max_tiles(pairs, e, big_rows),), torch.int32)
+            rows = big.numel() * big_rows
+            perm = ctx.scratch("moe_perm", (rows,), torch.int32)
+            inv = ctx.scratch("moe_inv", (pairs,), torch.int32)
+            K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles, align=big_rows,
+                        big=big, inv=inv, **routing)
+            xs = ctx.scratch("moe_xs", (rows, s.hidden), ctx.dtype)
+            K.moe_gather(x, perm, top, xs)
+            act = ctx.scratch("moe_act", (rows, s.intermediate), ctx.dtype)
+            K.moe_down_grouped_tc05(xs, self.wup.view(s.num_experts, s.intermediate, s.hidden), big, act)
+            K.unary_act(act, act, s.activation)
+            y16 = ctx.scratch("moe_y16", (rows, s.hidden), ctx.dtype)
+            K.moe_down_grouped_tc05(act, self.wdown.view(s.num_experts, s.hidden, s.intermediate), big, y16)
+            out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
+            K.moe_combine_rows(y16, inv, weights, out, top, extra=extra, **same)
+            return out
+        K.moe_route(logits, top, s.renormalize, ids, weights, offsets, perm, plan, max_tiles, **routing)
         act = ctx.scratch("moe_act", (pairs, s.intermediate), ctx.dtype)
         K.moe_up(x, self.wup.view(s.num_experts, s.intermediate, s.hidden), perm, offsets, plan, max_tiles, top,
                  s.activation, act, gated=False)
         y = ctx.scratch("moe_y", (pairs, s.hidden), torch.float32)
         K.moe_down(act, self.wdown.view(s.num_experts, s.hidden, s.intermediate), perm, offsets, plan, max_tiles, y)
         out = ctx.scratch("ffn_out", (n, s.hidden), ctx.dtype)
-        if s.identity_experts:
-            K.moe_combine(y, weights, out, top, extra=extra, ids=ids, x=x, num_real=s.num_experts)
-        else:
-            K.moe_combine(y, weights, out, top, extra=extra)
+        K.moe_combine(y, weights, out, top, extra=extra, **same)
         return out
