@@ -82,16 +82,18 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
 // Two kernels.  ems::delta_prep_kernel computes, once per token, what the recurrence reads: q and k of
 // every q / k head (activation, unit norm, the query's scale), k . q, the decay of every head and key
 // channel, and beta; all 32-bit, in a work buffer [N, 2 HK D + H D + HK + H] (q | k | g | k.q | beta).
-// ems::delta_recurrence_kernel then walks the tokens: as in the matrix memory of recurrent.cu, a block of
-// 16 warps owns a group of columns of one head's S ([D, V]) for one request; a column is shared by SL
-// lanes, lane s holding rows i * 4 SL + 4 s + e of the column in registers.  Tiles of 32 tokens of q, k
+// ems::delta_recurrence_kernel then walks the tokens: as in the matrix memory of recurrent.cu, a block
+// owns a group of columns of one head's S ([D, V]) for one request; a column is shared by SL
+// lanes, lane s holding rows i * 4 SL + 4 s + e of the column in registers, and a lane holds its rows of
+// two columns, so that the rows of q, k and g it reads from shared memory serve both.  Tiles of 32 tokens of q, k
 // and g are copied into shared memory with cp.async, the next tile while this one is computed.  A
 // column's update needs S^T k before it can write, so that dot product closes with shuffles for every
 // token; the read o = S^T q = (g S)^T q + u (k.q) is linear in what a lane holds, so the lanes' shares
 // are summed once per tile.
 
-constexpr int DR_WARPS = 16;
+constexpr int DR_WARPS = 8;
 constexpr int DR_TT = 32;
+constexpr int DR_CPL = 2;   // columns of S per lane: what a lane reads of q, k and g serves both
 
 struct DeltaParams {
     const void* q; const void* k; const void* v;   // [N, ld*] views; q/k head j begins at column j * D, v head h at h * V
@@ -169,7 +171,8 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
     constexpr int THREADS = DR_WARPS * 32;
     constexpr int DP = SL * DPT;
     constexpr int WCOLS = 32 / SL;
-    constexpr int COLS = DR_WARPS * WCOLS;
+    constexpr int GCOLS = DR_WARPS * WCOLS;                   // columns of one pass over the warps
+    constexpr int COLS = GCOLS * DR_CPL;                      // columns of a block
     constexpr int STAGE = 3 * TT * DP + TT * COLS + 2 * TT;   // floats of one stage
     extern __shared__ __align__(16) float smem[];
     const int D = p.D, V = p.V;
@@ -179,15 +182,17 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
     if (qlen <= 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slice = lane & (SL - 1), colw = lane / SL;
-    const int lcol = warp * WCOLS + colw;
-    const int col = blockIdx.x * COLS + lcol;
-    const bool live = col < V;
+    const int lcol = warp * WCOLS + colw;                      // this lane's first column inside the block
     float* st = p.state + ((size_t)p.slots[row] * p.H + head) * ((size_t)D * V);
-    float S[DPT];
+    float S[DR_CPL][DPT];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-        const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
-        S[i] = (live && d < D) ? st[(size_t)d * V + col] : 0.f;
+    for (int c = 0; c < DR_CPL; ++c) {
+        const int col = blockIdx.x * COLS + lcol + c * GCOLS;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
+            S[c][i] = (col < V && d < D) ? st[(size_t)d * V + col] : 0.f;
+        }
     }
     const T* vg = reinterpret_cast<const T*>(p.v) + (size_t)head * V;
     const size_t off_q = (size_t)kh * D, off_k = (size_t)p.HK * D + (size_t)kh * D;
@@ -211,9 +216,8 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
                 const float* w = p.work + (size_t)(q0 + t0 + (ok ? t : 0)) * p.work_ld + (ok ? d : 0);
                 dr_cp16(qs + t * DP + d, w + off_q, ok);
                 dr_cp16(ks + t * DP + d, w + off_k, ok);
-                if (t < cnt && d >= D) *reinterpret_cast<float4*>(gs + t * DP + d) = make_float4(1.f, 1.f, 1.f, 1.f);
-                else if (t >= cnt) *reinterpret_cast<float4*>(gs + t * DP + d) = make_float4(1.f, 1.f, 1.f, 1.f);
-                else dr_cp16(gs + t * DP + d, w + off_g, true);
+                if (ok) dr_cp16(gs + t * DP + d, w + off_g, true);
+                else *reinterpret_cast<float4*>(gs + t * DP + d) = make_float4(1.f, 1.f, 1.f, 1.f);
             }
         } else {
             for (int idx = threadIdx.x; idx < TT * DP; idx += THREADS) {
@@ -255,69 +259,93 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
         const float* vs = gs + TT * DP;
         const float* bs = vs + TT * COLS;
         const float* kqs = bs + TT;
-        float acc[TT];
+        // A lane reads its rows of q, k and g once per token and uses them for each of its DR_CPL columns.
+        float acc[DR_CPL][TT];
 #pragma unroll
         for (int t = 0; t < TT; ++t) {
             const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP) + slice;
             const float4* q4 = reinterpret_cast<const float4*>(qs + t * DP) + slice;
             const float4* g4 = reinterpret_cast<const float4*>(gs + t * DP) + slice;
-            float dk0 = 0.f, dk1 = 0.f, dq0 = 0.f, dq1 = 0.f;
+            float dk[DR_CPL], dq[DR_CPL], dk1[DR_CPL], dq1[DR_CPL];   // (two partial sums each: shorter chains)
+#pragma unroll
+            for (int c = 0; c < DR_CPL; ++c) dk[c] = dq[c] = dk1[c] = dq1[c] = 0.f;
+            float4 kk[DPT / 4];
 #pragma unroll
             for (int i = 0; i < DPT / 4; ++i) {
-                const float4 kk = k4[i * SL], qq = q4[i * SL], gg = g4[i * SL];
-                S[4 * i + 0] *= gg.x;
-                S[4 * i + 1] *= gg.y;
-                S[4 * i + 2] *= gg.z;
-                S[4 * i + 3] *= gg.w;
-                dk0 = fmaf(S[4 * i + 0], kk.x, dk0);
-                dk1 = fmaf(S[4 * i + 1], kk.y, dk1);
-                dk0 = fmaf(S[4 * i + 2], kk.z, dk0);
-                dk1 = fmaf(S[4 * i + 3], kk.w, dk1);
-                dq0 = fmaf(S[4 * i + 0], qq.x, dq0);
-                dq1 = fmaf(S[4 * i + 1], qq.y, dq1);
-                dq0 = fmaf(S[4 * i + 2], qq.z, dq0);
-                dq1 = fmaf(S[4 * i + 3], qq.w, dq1);
-            }
-            float dk = dk0 + dk1;
+                const float4 qq = q4[i * SL], gg = g4[i * SL];
+                kk[i] = k4[i * SL];
 #pragma unroll
-            for (int off = SL / 2; off >= 1; off >>= 1) dk += __shfl_xor_sync(0xffffffffu, dk, off);
-            const float u = bs[t] * (vs[t * COLS + lcol] - dk);
-#pragma unroll
-            for (int i = 0; i < DPT / 4; ++i) {
-                const float4 kk = k4[i * SL];
-                S[4 * i + 0] = fmaf(kk.x, u, S[4 * i + 0]);
-                S[4 * i + 1] = fmaf(kk.y, u, S[4 * i + 1]);
-                S[4 * i + 2] = fmaf(kk.z, u, S[4 * i + 2]);
-                S[4 * i + 3] = fmaf(kk.w, u, S[4 * i + 3]);
+                for (int c = 0; c < DR_CPL; ++c) {
+                    S[c][4 * i + 0] *= gg.x;
+                    S[c][4 * i + 1] *= gg.y;
+                    S[c][4 * i + 2] *= gg.z;
+                    S[c][4 * i + 3] *= gg.w;
+                    dk[c] = fmaf(S[c][4 * i + 0], kk[i].x, dk[c]);
+                    dq[c] = fmaf(S[c][4 * i + 0], qq.x, dq[c]);
+                    dk1[c] = fmaf(S[c][4 * i + 1], kk[i].y, dk1[c]);
+                    dq1[c] = fmaf(S[c][4 * i + 1], qq.y, dq1[c]);
+                    dk[c] = fmaf(S[c][4 * i + 2], kk[i].z, dk[c]);
+                    dq[c] = fmaf(S[c][4 * i + 2], qq.z, dq[c]);
+                    dk1[c] = fmaf(S[c][4 * i + 3], kk[i].w, dk1[c]);
+                    dq1[c] = fmaf(S[c][4 * i + 3], qq.w, dq1[c]);
+                }
             }
-            acc[t] = (dq0 + dq1) + (slice == 0 ? u * kqs[t] : 0.f);
+#pragma unroll
+            for (int c = 0; c < DR_CPL; ++c) {
+                dk[c] += dk1[c];
+                dq[c] += dq1[c];
+            }
+#pragma unroll
+            for (int off = SL / 2; off >= 1; off >>= 1)
+#pragma unroll
+                for (int c = 0; c < DR_CPL; ++c) dk[c] += __shfl_xor_sync(0xffffffffu, dk[c], off);
+            const float beta = bs[t], kq = kqs[t];
+#pragma unroll
+            for (int c = 0; c < DR_CPL; ++c) {
+                const float u = beta * (vs[t * COLS + lcol + c * GCOLS] - dk[c]);
+#pragma unroll
+                for (int i = 0; i < DPT / 4; ++i) {
+                    S[c][4 * i + 0] = fmaf(kk[i].x, u, S[c][4 * i + 0]);
+                    S[c][4 * i + 1] = fmaf(kk[i].y, u, S[c][4 * i + 1]);
+                    S[c][4 * i + 2] = fmaf(kk[i].z, u, S[c][4 * i + 2]);
+                    S[c][4 * i + 3] = fmaf(kk[i].w, u, S[c][4 * i + 3]);
+                }
+                acc[c][t] = dq[c] + (slice == 0 ? u * kq : 0.f);
+            }
         }
         // the lanes' shares of the reads, summed once per tile (a lane hands one half of what it holds to
         // its partner and adds the partner's other half)
 #pragma unroll
-        for (int off = SL / 2, n = TT; off >= 1; off >>= 1, n >>= 1) {
-            const bool upper = (lane & off) != 0;
+        for (int c = 0; c < DR_CPL; ++c) {
 #pragma unroll
-            for (int j = 0; j < n / 2; ++j) {
-                const float send = upper ? acc[j] : acc[j + n / 2];
-                const float keep = upper ? acc[j + n / 2] : acc[j];
-                acc[j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            for (int off = SL / 2, n = TT; off >= 1; off >>= 1, n >>= 1) {
+                const bool upper = (lane & off) != 0;
+#pragma unroll
+                for (int j = 0; j < n / 2; ++j) {
+                    const float send = upper ? acc[c][j] : acc[c][j + n / 2];
+                    const float keep = upper ? acc[c][j + n / 2] : acc[c][j];
+                    acc[c][j] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
             }
-        }
-        if (live) {
+            const int col = blockIdx.x * COLS + lcol + c * GCOLS;
+            if (col < V) {
 #pragma unroll
-            for (int j = 0; j < TT / SL; ++j) {
-                const int t = slice * (TT / SL) + j;
-                if (t < cnt) p.out[(size_t)(q0 + t0 + t) * ((size_t)p.H * V) + (size_t)head * V + col] = acc[j];
+                for (int j = 0; j < TT / SL; ++j) {
+                    const int t = slice * (TT / SL) + j;
+                    if (t < cnt) p.out[(size_t)(q0 + t0 + t) * ((size_t)p.H * V) + (size_t)head * V + col] = acc[c][j];
+                }
             }
         }
         __syncthreads();  // this tile is consumed before the stage after next overwrites it
     }
-    if (live) {
+#pragma unroll
+    for (int c = 0; c < DR_CPL; ++c) {
+        const int col = blockIdx.x * COLS + lcol + c * GCOLS;
+        if (col >= V) continue;
 #pragma unroll
         for (int i = 0; i < DPT; ++i) {
             const int d = (i / 4) * (4 * SL) + 4 * slice + (i & 3);
-            if (d < D) st[(size_t)d * V + col] = S[i];
+            if (d < D) st[(size_t)d * V + col] = S[c][i];
         }
     }
 }
@@ -373,7 +401,7 @@ __global__ void __launch_bounds__(128) delta_step_kernel(const DeltaParams p) {
 
 template <typename T, int DPT, int SL>
 static int launch_delta_as(const DeltaParams& p, int rows, cudaStream_t stream) {
-    constexpr int COLS = DR_WARPS * (32 / SL);
+    constexpr int COLS = DR_WARPS * (32 / SL) * DR_CPL;
     const dim3 grid((p.V + COLS - 1) / COLS, p.H, rows);
     const size_t smem = sizeof(float) * 2 * ((size_t)DR_TT * (3 * SL * DPT + COLS) + 2 * DR_TT);
     auto kernel = delta_recurrence_kernel<T, DPT, SL>;
@@ -395,9 +423,29 @@ static int launch_delta(DeltaParams& p, int rows, int N, cudaStream_t stream) {
     }
     // 16-byte copies of four floats where every row of the work buffer begins aligned
     p.vec_ok = p.D % 4 == 0 && p.work_ld % 4 == 0 && ((uintptr_t)p.work % 16) == 0;
+    // Few lanes per column mean short reductions, and the lanes of a warp that hold the same rows of several
+    // columns read q, k and g as one broadcast: 1.6 times the columns per SM and microsecond at D = 128.  But a
+    // block then owns more columns, and a step of one or two requests leaves SMs idle; such steps spread a
+    // column over more lanes (measured at 16 heads of 128 x 128, one prompt of 2048 tokens: 509 us over 128
+    // blocks against 626 us over 64).
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    auto blocks = [&](int cols) { return (long long)rows * p.H * ((p.V + cols - 1) / cols); };
     if (p.D <= 32) return launch_delta_as<T, 4, 8>(p, rows, stream);
-    if (p.D <= 64) return launch_delta_as<T, 4, 16>(p, rows, stream);
-    if (p.D <= 128) return launch_delta_as<T, 4, 32>(p, rows, stream);
+    if (p.D <= 64) {
+        if (blocks(DR_WARPS * 4 * DR_CPL) >= sms) return launch_delta_as<T, 8, 8>(p, rows, stream);
+        return launch_delta_as<T, 4, 16>(p, rows, stream);
+    }
+    if (p.D <= 128) {
+        if (blocks(DR_WARPS * 2 * DR_CPL) >= sms) return launch_delta_as<T, 8, 16>(p, rows, stream);
+        return launch_delta_as<T, 4, 32>(p, rows, stream);
+    }
+    if (blocks(DR_WARPS * 2 * DR_CPL) >= sms) return launch_delta_as<T, 16, 16>(p, rows, stream);
     return launch_delta_as<T, 8, 32>(p, rows, stream);
 }
 
