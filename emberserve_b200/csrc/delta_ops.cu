@@ -427,7 +427,7 @@ static int launch_delta(DeltaParams& p, int rows, int N, cudaStream_t stream) {
     // columns read q, k and g as one broadcast: 1.6 times the columns per SM and microsecond at D = 128.  But a
     // block then owns more columns, and a step of one or two requests leaves SMs idle; such steps spread a
     // column over more lanes (measured at 16 heads of 128 x 128, one prompt of 2048 tokens: 509 us over 128
-    // blocks against 626 us over 64).
+    // blocks against 626 us over 64; at 32 heads the 256 blocks of the wide tiling are two waves, 1090 us).
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -435,17 +435,22 @@ static int launch_delta(DeltaParams& p, int rows, int N, cudaStream_t stream) {
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             sms = 148;
     }
-    auto blocks = [&](int cols) { return (long long)rows * p.H * ((p.V + cols - 1) / cols); };
+    // waves of blocks over the SMs, the narrow tiling's wave taken as a quarter longer
+    auto narrow = [&](int cols_narrow) {
+        const long long bn = (long long)rows * p.H * ((p.V + cols_narrow - 1) / cols_narrow);
+        const long long bw = (long long)rows * p.H * ((p.V + cols_narrow / 2 - 1) / (cols_narrow / 2));
+        return 5 * ((bn + sms - 1) / sms) < 4 * ((bw + sms - 1) / sms);
+    };
     if (p.D <= 32) return launch_delta_as<T, 4, 8>(p, rows, stream);
     if (p.D <= 64) {
-        if (blocks(DR_WARPS * 4 * DR_CPL) >= sms) return launch_delta_as<T, 8, 8>(p, rows, stream);
+        if (narrow(DR_WARPS * 4 * DR_CPL)) return launch_delta_as<T, 8, 8>(p, rows, stream);
         return launch_delta_as<T, 4, 16>(p, rows, stream);
     }
     if (p.D <= 128) {
-        if (blocks(DR_WARPS * 2 * DR_CPL) >= sms) return launch_delta_as<T, 8, 16>(p, rows, stream);
+        if (narrow(DR_WARPS * 2 * DR_CPL)) return launch_delta_as<T, 8, 16>(p, rows, stream);
         return launch_delta_as<T, 4, 32>(p, rows, stream);
     }
-    if (blocks(DR_WARPS * 2 * DR_CPL) >= sms) return launch_delta_as<T, 16, 16>(p, rows, stream);
+    if (narrow(DR_WARPS * 2 * DR_CPL)) return launch_delta_as<T, 16, 16>(p, rows, stream);
     return launch_delta_as<T, 8, 32>(p, rows, stream);
 }
 

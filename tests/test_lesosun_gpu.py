@@ -293,7 +293,7 @@ def test_state_space_gates_and_gated_norm(dtype):
 @pytest.mark.parametrize("h,hk,d,v", [(4, 2, 8, 12), (3, 3, 33, 70), (1, 1, 8, 8), (6, 1, 4, 40), (2, 2, 64, 64),
                                        (4, 2, 128, 128), (2, 1, 200, 24),
                                        # enough blocks for the tilings with fewer lanes per column
-                                       (80, 40, 128, 32), (96, 2, 64, 16), (80, 1, 200, 16)])
+                                       (80, 40, 128, 32), (96, 2, 64, 64), (80, 1, 200, 32)])
 @DTYPES
 def test_delta_rule_memory_in_portions_through_slots_with_stale_contents(dtype, h, hk, d, v):
     g = torch.Generator().manual_seed(h * d + v)
