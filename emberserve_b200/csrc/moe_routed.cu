@@ -542,6 +542,40 @@ __global__ void moe_combine_rows_kernel(const bf16* __restrict__ y, const int* _
     }
 }
 
+// The same, eight columns per thread and 16 bytes per load (H a multiple of 8, 16-byte aligned rows); a token's
+// choices are added in the same order.
+__global__ void moe_combine_rows_vec_kernel(const bf16* __restrict__ y, const int* __restrict__ inv,
+                                            const float* __restrict__ wts, bf16* __restrict__ out, int top, int H,
+                                            const bf16* __restrict__ extra, const int* __restrict__ ids,
+                                            const bf16* __restrict__ x, int num_real) {
+    const size_t t = blockIdx.x;
+    for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+        float s[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j] = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const bool same = ids && ids[t * top + k] >= num_real;
+            const bf16* src = same ? x + t * H + c : y + (size_t)inv[t * top + k] * H + c;
+            const uint4 raw = *reinterpret_cast<const uint4*>(src);
+            const bf16* e = reinterpret_cast<const bf16*>(&raw);
+            const float w = wts ? wts[t * top + k] : 1.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] = fmaf(w, __bfloat162float(e[j]), s[j]);
+        }
+        if (extra) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(extra + t * H + c);
+            const bf16* e = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] += __bfloat162float(e[j]);
+        }
+        uint4 packed;
+        bf16* o = reinterpret_cast<bf16*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(s[j]);
+        *reinterpret_cast<uint4*>(out + t * H + c) = packed;
+    }
+}
+
 }  // namespace ems
 
 using namespace ems;
@@ -551,6 +585,13 @@ EMS_EXPORT int ems_moe_combine_rows(const void* y, const int* inv, const float* 
                                     cudaStream_t stream) {
     if (n <= 0) return EMS_OK;
     int th = 32;
+    const uintptr_t bits = (uintptr_t)y | (uintptr_t)out | (uintptr_t)extra | (uintptr_t)x;
+    if (H % 8 == 0 && (bits & 15) == 0) {
+        while (th * 8 < H && th < 256) th <<= 1;
+        moe_combine_rows_vec_kernel<<<n, th, 0, stream>>>((const bf16*)y, inv, wts, (bf16*)out, top, H,
+                                                          (const bf16*)extra, x ? ids : nullptr, (const bf16*)x, num_real);
+        return launch_status();
+    }
     while (th < H && th < 256) th <<= 1;
     moe_combine_rows_kernel<<<n, th, 0, stream>>>((const bf16*)y, inv, wts, (bf16*)out, top, H, (const bf16*)extra,
                                                   x ? ids : nullptr, (const bf16*)x, num_real);
