@@ -288,54 +288,6 @@ __global__ void causal_taps_kernel(const T* __restrict__ x, long long ldx, const
     }
 }
 
-// The same with 16 bytes per load: a thread owns VEC consecutive channels (C, ldx multiples of VEC, 16-byte
-// aligned rows).  Every channel's sum is formed in the same order as above.
-template <typename T>
-__global__ void causal_taps_vec_kernel(const T* __restrict__ x, long long ldx, const void* __restrict__ w, int w_dtype,
-                                       const void* __restrict__ bias, int identity,
-                                       const float* __restrict__ state, const int* __restrict__ slots,
-                                       const int* __restrict__ cu_q, const int* __restrict__ row_of_token,
-                                       T* __restrict__ out, int C, int taps) {
-    constexpr int VEC = 16 / sizeof(T);
-    const int t = blockIdx.x;
-    const int row = row_of_token[t];
-    const int first = cu_q[row];
-    const int local = t - first;
-    const float* st = state ? state + (size_t)slots[row] * (taps - 1) * C : nullptr;
-    for (int c = threadIdx.x * VEC; c < C; c += blockDim.x * VEC) {
-        float conv[VEC];
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) conv[i] = bias ? load_any(bias, w_dtype, c + i) : 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int s = local - (taps - 1) + j;
-            float v[VEC];
-            if (s >= 0) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(first + s) * ldx + c);
-                const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) v[i] = to_f32<T>(e[i]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) v[i] = st ? st[(size_t)(taps - 1 + s) * C + c + i] : 0.f;
-            }
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) conv[i] += load_any(w, w_dtype, (size_t)(c + i) * taps + j) * v[i];
-        }
-        uint4 packed;
-        T* o = reinterpret_cast<T*>(&packed);
-        if (identity) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + c);
-            const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) o[i] = from_f32<T>(to_f32<T>(e[i]) + conv[i]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) o[i] = from_f32<T>(conv[i]);
-        }
-        *reinterpret_cast<uint4*>(out + (size_t)t * C + c) = packed;
-    }
-}
-
 // After the convolution has read the old state: the last taps - 1 inputs of every row, from the
 // step's tokens and, where the row brought fewer, from the old state moved up.  A thread owns a
 // channel, reads entries above the one it writes, and so needs no second buffer.
@@ -478,9 +430,6 @@ EMS_EXPORT int ems_causal_taps(const void* x, long long ldx, const void* w, int 
     if (n <= 0) return EMS_OK;
     if (taps < 1 || (taps > 1 && !state) || ldx < C) return EMS_ERR_SHAPE;
     const int th = threads_for(C);
-    // 16 bytes per load where every row begins aligned and holds whole vectors
-    const int per = dtype == EMS_F32 ? 4 : 8;
-    const bool vec_ok = C % per == 0 && ldx % per == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0;
 #define EMS_LAUNCH_TAPS(T)                                                                                   \
     do {                                                                                                     \
         if (n == rows && taps > 1) {                                                                         \
@@ -490,14 +439,6 @@ EMS_EXPORT int ems_causal_taps(const void* x, long long ldx, const void* w, int 
                                                                   slots, (T*)out, C, taps);                  \
             break;                                                                                           \
         }                                                                                                    \
-        if (vec_ok) {                                                                                        \
-            constexpr int VEC = 16 / (int)sizeof(T);                                                         \
-            int tv = 32;                                                                                     \
-            while (tv * VEC < C && tv < 256) tv <<= 1;                                                       \
-            causal_taps_vec_kernel<T><<<n, tv, 0, stream>>>((const T*)x, ldx, w, w_dtype, bias, identity,    \
-                                                            (const float*)state, slots,                     \
-                                                            cu_q, row_of_token, (T*)out, C, taps);          \
-        } else                                                                                               \
         causal_taps_kernel<T><<<n, th, 0, stream>>>((const T*)x, ldx, w, w_dtype, bias, identity,            \
                                                     (const float*)state, slots,                             \
                                                     cu_q, row_of_token, (T*)out, C, taps);                  \
