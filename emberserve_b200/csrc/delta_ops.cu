@@ -81,7 +81,8 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
 //
 // Two kernels.  ems::delta_prep_kernel computes, once per token, what the recurrence reads: q and k of
 // every q / k head (activation, unit norm, the query's scale), k . q, the decay of every head and key
-// channel, and beta; all 32-bit, in a work buffer [N, 2 HK D + H D + HK + H] (q | k | g | k.q | beta).
+// channel, beta, and the activation of v; all 32-bit, in a work buffer [N, 2 HK D + H D + H V + HK + H]
+// (q | k | g | v | k.q | beta).
 // ems::delta_recurrence_kernel then walks the tokens: as in the matrix memory of recurrent.cu, a block
 // owns a group of columns of one head's S ([D, V]) for one request; a column is shared by SL
 // lanes, lane s holding rows i * 4 SL + 4 s + e of the column in registers, and a lane holds its rows of
@@ -104,7 +105,7 @@ struct DeltaParams {
     const void* g_bias;        // [H * D]
     const void* a_log;         // [H]: g = exp(-exp(a_log[h]) * softplus(g_raw + g_bias))
     int p_dtype;               // element type of g_bias and a_log
-    float* work;               // [N, work_ld]: q [HK * D] | k [HK * D] | g [H * D] | k.q [HK] | beta [H]
+    float* work;               // [N, work_ld]: q [HK * D] | k [HK * D] | g [H * D] | v [H * V] | k.q [HK] | beta [H]
     int work_ld;
     float* state;              // [slots, H, D * V]
     const int* slots; const int* cu_q;
@@ -124,8 +125,13 @@ __global__ void delta_prep_kernel(const DeltaParams p) {
     float* wq = w;
     float* wk = wq + (size_t)p.HK * D;
     float* wg = wk + (size_t)p.HK * D;
-    float* wkq = wg + (size_t)p.H * D;
+    float* wv = wg + (size_t)p.H * D;
+    float* wkq = wv + (size_t)p.H * p.V;
     float* wb = wkq + p.HK;
+    {
+        const T* vg = reinterpret_cast<const T*>(p.v) + (size_t)tok * p.ldv;
+        for (int c = threadIdx.x; c < p.H * p.V; c += blockDim.x) wv[c] = dr_in(to_f32<T>(vg[c]), p.act);
+    }
     for (int j = warp; j < p.HK + p.H; j += nwarps) {
         if (j < p.HK) {
             const T* qg = reinterpret_cast<const T*>(p.q) + (size_t)tok * p.ldq + (size_t)j * D;
@@ -157,6 +163,12 @@ __global__ void delta_prep_kernel(const DeltaParams p) {
             if (lane == 0) wb[h] = d_sigmoid(to_f32<T>(reinterpret_cast<const T*>(p.beta)[(size_t)tok * p.ldb + h]));
         }
     }
+}
+
+__device__ __forceinline__ void dr_cp4(float* dst, const float* src, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 4 : 0;   // (0: the word is filled with zeros)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
 }
 
 __device__ __forceinline__ void dr_cp16(float* dst, const float* src, bool valid) {
@@ -194,10 +206,11 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
             S[c][i] = (col < V && d < D) ? st[(size_t)d * V + col] : 0.f;
         }
     }
-    const T* vg = reinterpret_cast<const T*>(p.v) + (size_t)head * V;
     const size_t off_q = (size_t)kh * D, off_k = (size_t)p.HK * D + (size_t)kh * D;
     const size_t off_g = 2 * (size_t)p.HK * D + (size_t)head * D;
-    const size_t off_kq = 2 * (size_t)p.HK * D + (size_t)p.H * D + kh, off_b = 2 * (size_t)p.HK * D + (size_t)p.H * D + p.HK + head;
+    const size_t off_v = 2 * (size_t)p.HK * D + (size_t)p.H * D + (size_t)head * V + (size_t)blockIdx.x * COLS;
+    const size_t off_kq = 2 * (size_t)p.HK * D + (size_t)p.H * D + (size_t)p.H * V + kh;
+    const size_t off_b = 2 * (size_t)p.HK * D + (size_t)p.H * D + (size_t)p.H * V + p.HK + head;
 
     // Stage the tile that begins at token t0: q, k, g rows (zeros past D; tokens past the end hold q = k = 0,
     // g = 1, beta = 0: nothing changes), v of this block's columns, k.q and beta.
@@ -229,17 +242,33 @@ __global__ void __launch_bounds__(DR_WARPS * 32) delta_recurrence_kernel(const D
                 gs[idx] = ok ? w[off_g] : 1.f;
             }
         }
+        if (p.vec_ok) {   // (V is a multiple of 4 then: a group of four columns lies inside the head or outside)
+            for (int idx = threadIdx.x; idx < TT * (COLS / 4); idx += THREADS) {
+                const int t = idx / (COLS / 4), c = (idx % (COLS / 4)) * 4;
+                const bool ok = t < cnt && (int)(blockIdx.x * COLS) + c < V;
+                const float* w = p.work + (size_t)(q0 + t0 + (ok ? t : 0)) * p.work_ld + off_v + (ok ? c : 0);
+                dr_cp16(vs + t * COLS + c, ok ? w : p.work, ok);
+            }
+            if ((int)threadIdx.x < 2 * TT) {
+                const int t = threadIdx.x % TT;
+                const bool ok = t < cnt;
+                const float* w = p.work + (size_t)(q0 + t0 + (ok ? t : 0)) * p.work_ld;
+                dr_cp4((int)threadIdx.x < TT ? bs + t : kqs + t, w + ((int)threadIdx.x < TT ? off_b : off_kq), ok);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < TT * COLS; idx += THREADS) {
+                const int t = idx / COLS, c = idx % COLS;
+                const bool ok = t < cnt && (int)(blockIdx.x * COLS) + c < V;
+                vs[idx] = ok ? p.work[(size_t)(q0 + t0 + t) * p.work_ld + off_v + c] : 0.f;
+            }
+            if ((int)threadIdx.x < TT) {
+                const int t = threadIdx.x;
+                const float* w = p.work + (size_t)(q0 + t0 + (t < cnt ? t : 0)) * p.work_ld;
+                bs[t] = t < cnt ? w[off_b] : 0.f;
+                kqs[t] = t < cnt ? w[off_kq] : 0.f;
+            }
+        }
         asm volatile("cp.async.commit_group;\n" ::);
-        for (int idx = threadIdx.x; idx < TT * COLS; idx += THREADS) {
-            const int t = idx / COLS, gc = blockIdx.x * COLS + idx % COLS;
-            vs[idx] = (t < cnt && gc < V) ? dr_in(to_f32<T>(vg[(size_t)(q0 + t0 + t) * p.ldv + gc]), p.act) : 0.f;
-        }
-        if ((int)threadIdx.x < TT) {
-            const int t = threadIdx.x;
-            const float* w = p.work + (size_t)(q0 + t0 + (t < cnt ? t : 0)) * p.work_ld;
-            bs[t] = t < cnt ? w[off_b] : 0.f;
-            kqs[t] = t < cnt ? w[off_kq] : 0.f;
-        }
     };
 
     stage(0, smem);
@@ -371,8 +400,8 @@ __global__ void __launch_bounds__(128) delta_step_kernel(const DeltaParams p) {
     __syncthreads();
     const int col = blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= V) return;
-    const float beta = w[2 * (size_t)p.HK * D + (size_t)p.H * D + p.HK + head];
-    const float vj = dr_in(to_f32<T>(reinterpret_cast<const T*>(p.v)[(size_t)tok * p.ldv + (size_t)head * V + col]), p.act);
+    const float beta = w[2 * (size_t)p.HK * D + (size_t)p.H * D + (size_t)p.H * V + p.HK + head];
+    const float vj = w[2 * (size_t)p.HK * D + (size_t)p.H * D + (size_t)head * V + col];
     float* sp = p.state + ((size_t)p.slots[tok] * p.H + head) * ((size_t)D * V) + col;
     float dk0 = 0.f, dk1 = 0.f;
     int d = 0;
@@ -422,7 +451,7 @@ static int launch_delta(DeltaParams& p, int rows, int N, cudaStream_t stream) {
         return launch_status();
     }
     // 16-byte copies of four floats where every row of the work buffer begins aligned
-    p.vec_ok = p.D % 4 == 0 && p.work_ld % 4 == 0 && ((uintptr_t)p.work % 16) == 0;
+    p.vec_ok = p.D % 4 == 0 && p.V % 4 == 0 && p.work_ld % 4 == 0 && ((uintptr_t)p.work % 16) == 0;
     // Few lanes per column mean short reductions, and the lanes of a warp that hold the same rows of several
     // columns read q, k and g as one broadcast: 1.6 times the columns per SM and microsecond at D = 128.  But a
     // block then owns more columns, and a step of one or two requests leaves SMs idle; such steps spread a
@@ -573,8 +602,8 @@ EMS_EXPORT int ems_delta_recurrence(const void* q, long long ldq, const void* k,
                                     long long work_floats, cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return EMS_OK;
     if (H <= 0 || HK <= 0 || H % HK || D <= 0 || D > 256 || V <= 0 || H > 65535 || rows > 65535) return EMS_ERR_SHAPE;
-    // a row of the work buffer: q | k | g | k.q | beta, rounded up to a multiple of four floats
-    const int work_ld = (2 * HK * D + H * D + HK + H + 3) / 4 * 4;
+    // a row of the work buffer: q | k | g | v | k.q | beta, rounded up to a multiple of four floats
+    const int work_ld = (2 * HK * D + H * D + H * V + HK + H + 3) / 4 * 4;
     if (!work || work_floats < (long long)N * work_ld) return EMS_ERR_SCRATCH;
     DeltaParams p;
     p.q = q; p.k = k; p.v = v; p.ldq = ldq; p.ldk = ldk; p.ldv = ldv; p.beta = beta; p.ldb = ldb; p.g_raw = g_raw;
@@ -587,8 +616,8 @@ EMS_EXPORT int ems_delta_recurrence(const void* q, long long ldq, const void* k,
 }
 
 // floats of the work buffer that ems_delta_recurrence needs for N tokens
-EMS_EXPORT long long ems_delta_work_floats(int N, int H, int HK, int D) {
-    return (long long)N * ((2 * HK * D + H * D + HK + H + 3) / 4 * 4);
+EMS_EXPORT long long ems_delta_work_floats(int N, int H, int HK, int D, int V) {
+    return (long long)N * ((2 * HK * D + H * D + H * V + HK + H + 3) / 4 * 4);
 }
 
 EMS_EXPORT int ems_ssm_gates(const void* x, long long ldx, int dtype, const void* bias, const void* a_log, int p_dtype,

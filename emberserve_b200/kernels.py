@@ -125,7 +125,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ems_latent_attention_scratch_bytes.restype = c_longlong
     lib.ems_moe_tile_rows.argtypes = []
     lib.ems_moe_tile_rows.restype = c_int
-    lib.ems_delta_work_floats.argtypes = [I, I, I, I]
+    lib.ems_delta_work_floats.argtypes = [I, I, I, I, I]
     lib.ems_delta_work_floats.restype = c_longlong
 
 
@@ -969,8 +969,8 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
     per head; q is multiplied by `q_scale`; beta_t = sigmoid(beta[t, h]); g_t = exp(-exp(a_log[h]) *
     softplus(g_raw[t, h * dim + d] + g_bias[h * dim + d])) with g_raw float32 [N, H * dim].  Head h reads
     q / k head h // (H / qk_heads).  state: float32 [slots, H, dim * vdim]; out: float32 [N, H * vdim].
-    `work`: float32, at least `delta_work_floats(N, H, qk_heads, dim)` elements, where a first kernel leaves
-    the prepared q, k, decays, k . q and beta of every token (allocated here when None)."""
+    `work`: float32, at least `delta_work_floats(N, H, qk_heads, dim, vdim)` elements, where a first kernel leaves
+    the prepared q, k, decays, v, k . q and beta of every token (allocated here when None)."""
     n = q.shape[0]
     assert q.stride(1) == k.stride(1) == v.stride(1) == beta.stride(1) == 1 and q.dtype == k.dtype == v.dtype == beta.dtype
     assert out.dtype == torch.float32 and out.shape == (n, num_heads * vdim) and out.is_contiguous()
@@ -980,7 +980,7 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
     if not q.is_cuda:
         raise KernelError("q must be a CUDA tensor (emberserve_b200 has no CPU path)")
     if work is None:
-        work = torch.empty(delta_work_floats(n, num_heads, qk_heads, dim), dtype=torch.float32, device=q.device)
+        work = torch.empty(delta_work_floats(n, num_heads, qk_heads, dim, vdim), dtype=torch.float32, device=q.device)
     _check(library().ems_delta_recurrence(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), beta.data_ptr(),
         beta.stride(0), _dt(q), MEMORY_INPUT_ACTIVATIONS[act], 0 if unit_eps is None else 1, float(unit_eps or 0.0),
@@ -989,9 +989,9 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
         _ptr(out, "out"), _f32(work, "work"), work.numel(), _stream()), "delta_recurrence", 2)
 
 
-def delta_work_floats(num_tokens: int, num_heads: int, qk_heads: int, dim: int) -> int:
+def delta_work_floats(num_tokens: int, num_heads: int, qk_heads: int, dim: int, vdim: int) -> int:
     """Elements of the float32 work buffer that `delta_recurrence` needs for `num_tokens` tokens."""
-    return int(library().ems_delta_work_floats(num_tokens, num_heads, qk_heads, dim))
+    return int(library().ems_delta_work_floats(num_tokens, num_heads, qk_heads, dim, vdim))
 
 
 def ssm_gates(x: torch.Tensor, bias: torch.Tensor, a_log: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> None:

@@ -465,8 +465,8 @@ class ChannelDelta(Mixer):
             prefix + ".conv", self.shared)
         self._conv_state = self.conv.cache_need()
         self._norm_rows: torch.Tensor | None = None
-        # 32-bit numbers per token that the memory kernel prepares: q | k | decays | k.q | beta, in fours
-        self._work_per_token = -(-(2 * self.qk + spec.num_heads * spec.dim + spec.qk_heads + spec.num_heads) // 4) * 4
+        # 32-bit numbers per token that the memory kernel prepares: q | k | decays | v | k.q | beta, in fours
+        self._work_per_token = -(-(2 * self.qk + spec.num_heads * spec.dim + self.vv + spec.qk_heads + spec.num_heads) // 4) * 4
 
     def children(self) -> dict[str, Part]:
         return {"conv": self.conv}
