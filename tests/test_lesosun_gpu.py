@@ -105,6 +105,36 @@ def test_erf_gelu(dtype, act):
     _close(out, want, dtype, act)
 
 
+@DTYPES
+@pytest.mark.parametrize("taps,identity,bias,c", [(1, False, False, 24), (2, False, True, 50), (4, False, False, 256),
+                                                  (3, True, True, 33), (8, False, True, 40), (9, False, False, 16)])
+def test_convolution_over_long_steps_through_slots_that_change_hands(dtype, taps, identity, bias, c):
+    """Steps of hundreds of tokens beside short ones, requests that begin and continue inside a step, a column
+    range of a wider buffer, one to nine taps, then single tokens."""
+    g = torch.Generator().manual_seed(taps * 100 + c)
+    w = (0.7 * torch.randn(c, taps, generator=g)).to(dtype)
+    b = torch.randn(c, generator=g).to(dtype) if bias else None
+    state_ref = torch.randn(5, max(taps - 1, 1), c, generator=g) if taps > 1 else None
+    if taps > 1:
+        state_ref[[0, 2, 4]] = 0  # the slots in use were zeroed when they were handed out
+    state = None if state_ref is None else state_ref.clone().to(DEV)
+    slots = _i32([2, 0, 4])
+    for step, lens in enumerate(([200, 3, 77], [1, 130, 31], [33, 1, 1], [1, 1, 1], [140, 2, 5])):
+        n = sum(lens)
+        wide = torch.randn(n, c + 6, generator=g).to(dtype)
+        cu = _i32(np.concatenate([[0], np.cumsum(lens)]))
+        row_of = _i32(np.repeat(np.arange(3), lens))
+        want = torch.zeros(n, c, dtype=dtype)
+        R.causal_taps(wide[:, 4:4 + c], w, state_ref, None if state_ref is None else slots.cpu(), cu.cpu(), row_of.cpu(),
+                      want, 3, bias=b, identity=identity)
+        got = torch.zeros(n, c, dtype=dtype, device=DEV)
+        _K().causal_taps(wide.to(DEV)[:, 4:4 + c], w.to(DEV), state, None if state is None else slots, cu, row_of, got, 3,
+                         bias=None if b is None else b.to(DEV), identity=identity)
+        _close(got, want, dtype, f"step {step}")
+    if taps > 1:
+        _close(state, state_ref, torch.float32, "state")
+
+
 def _paged(g, dtype, nkv, d, dv, page_size, ctx_lens):
     """Block tables over shuffled pages for requests of the given lengths; stale contents everywhere."""
     pages_per = [-(-c // page_size) for c in ctx_lens]
